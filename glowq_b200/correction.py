@@ -1,0 +1,219 @@
+"""Low-rank correction wrapper and patchers, same surface as GlowQ's step3 scripts
+(``AddSVDCorrection``, ``MiniGroupCache``, ``patch_svd_correction_wrappers``: src/step3_eval_dataset.py:417-605;
+``patch_svd_correction_wrappers_cumulative``, the GlowQ-S enable mask: src/restoration/step4_evaluate_cumulative.py:99-154).
+
+The reference wrapper runs ``inner(x)``, then ``F.linear(x, B_q)`` (or a cache hit), ``F.linear(r, A_q)`` and an
+in-place add: 3-4 launches.  Here the whole of ``z + alpha * (x B_q^T) A_q^T`` is ONE library launch per module: the
+wrapper only decides, from the role and the cache state, whether that launch computes r = B_q x and leaves it in the
+group's device buffer (roles q / gate / solo) or reads it from there (roles k / v / up on a hit)."""
+from __future__ import annotations
+
+import warnings
+import weakref
+from typing import Dict, Optional, Set
+
+import torch
+import torch.nn as nn
+
+from .cuda_w4a16 import kernels as K
+from .cuda_w4a16.linear import CudaW4A16Linear
+
+try:  # tqdm only decorates the patch loop, as in the reference
+    from tqdm import tqdm as _tqdm
+except Exception:  # noqa: BLE001
+    def _tqdm(it, **_):
+        return it
+
+_ALL_CACHES: "weakref.WeakSet[MiniGroupCache]" = weakref.WeakSet()
+
+
+def clear_group_cache() -> None:
+    """Invalidate every live group cache (a no-op placeholder in src/step3_eval_dataset.py:409-411)."""
+    for c in list(_ALL_CACHES):
+        c.clear()
+
+
+def _x_key(x: torch.Tensor):
+    return (x.data_ptr(), tuple(x.shape), x.dtype, x._version)
+
+
+class MiniGroupCache:
+    """Hand-off of r = B_shared . x between the members of a group (src/step3_eval_dataset.py:417-444):
+    the producer (q / gate) calls ``set(r, uses)``; each consumer (k, v / up) calls ``consume()`` and gets
+    ``(r, True)`` until ``uses`` run out.  Here r lives in a device buffer owned by the cache that the kernel
+    writes and reads directly.  A consumer may pass the identity of its input; a hit then also requires that
+    the producer saw the same tensor (the reference trusts call order alone)."""
+
+    __slots__ = ("r", "valid", "uses_left", "_key", "_buf", "__weakref__")
+
+    def __init__(self):
+        self.r: Optional[torch.Tensor] = None
+        self.valid: bool = False
+        self.uses_left: int = 0
+        self._key = None
+        self._buf: Optional[torch.Tensor] = None
+        _ALL_CACHES.add(self)
+
+    def buffer(self, m: int, rank: int, device) -> torch.Tensor:
+        b = self._buf
+        if b is None or b.device != device or b.size(1) != rank or b.size(0) < m:
+            self._buf = b = torch.empty((max(m, 16), rank), dtype=torch.float16, device=device)
+        return b[:m]
+
+    def set(self, r: torch.Tensor, uses: int, key=None):
+        self.r = r
+        self.valid = True
+        self.uses_left = uses
+        self._key = key
+
+    def consume(self, key=None):
+        if self.valid and self.uses_left > 0 and (key is None or self._key is None or key == self._key):
+            self.uses_left -= 1
+            out = self.r
+            if self.uses_left == 0:
+                self.valid = False
+                self.r = None
+            return out, True
+        return None, False
+
+    def clear(self):
+        self.r = None
+        self.valid = False
+        self.uses_left = 0
+        self._key = None
+
+
+class AddSVDCorrection(nn.Module):
+    """``inner(x) + alpha_svd * (x B_q^T) A_q^T`` (src/step3_eval_dataset.py:450-516), fused into one launch."""
+
+    def __init__(self, inner: nn.Module, A_q: torch.Tensor, B_q: torch.Tensor, role: str, is_group: bool,
+                 group_cache: Optional[MiniGroupCache], alpha_svd: float = 1.0):
+        super().__init__()
+        if not isinstance(inner, CudaW4A16Linear):
+            raise TypeError("AddSVDCorrection wraps CudaW4A16Linear modules only (no Triton / dense backends here)")
+        self.inner = inner
+        self.register_buffer("A_q", A_q.to(torch.float16).contiguous(), persistent=False)
+        self.register_buffer("B_q", B_q.to(torch.float16).contiguous(), persistent=False)
+        self.role = role
+        self.is_group = is_group
+        self.group_cache = group_cache
+        self.alpha_svd = alpha_svd
+        self._own_r: Optional[torch.Tensor] = None
+        # The reference discovers a factor/linear shape mismatch as a RuntimeError inside forward and then
+        # returns the uncorrected output (step3_eval_dataset.py:512-516); the same outcome, decided once, with a warning.
+        self._mismatch = (A_q.dim() != 2 or B_q.dim() != 2 or A_q.size(0) != inner.out_features
+                          or B_q.size(1) != inner.in_features or A_q.size(1) != B_q.size(0))
+        if self._mismatch:
+            warnings.warn(f"AddSVDCorrection: factor shapes A{tuple(A_q.shape)} B{tuple(B_q.shape)} do not fit "
+                          f"linear {inner.in_features}->{inner.out_features}; correction disabled for this module")
+
+    def _private_r(self, m: int, rank: int, device) -> torch.Tensor:
+        b = self._own_r
+        if b is None or b.device != device or b.size(1) != rank or b.size(0) < m:
+            self._own_r = b = torch.empty((max(m, 16), rank), dtype=torch.float16, device=device)
+        return b[:m]
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.alpha_svd == 0.0 or self._mismatch:
+            return self.inner(x)
+        inner = self.inner
+        lead = x.shape[:-1]
+        x2d = inner._flatten_input(x)
+        m, rank, dev = x2d.size(0), self.A_q.size(1), x2d.device
+        key = _x_key(x)
+        cache = self.group_cache if self.is_group else None
+        mode, r_buf = K.R_COMPUTE, None
+        if cache is not None and self.role in ("k", "v", "up"):
+            r_buf, hit = cache.consume(key)
+            if hit and r_buf is not None and r_buf.size(0) == m and r_buf.device == dev:
+                mode = K.R_LOAD
+            else:
+                r_buf = None
+        if r_buf is None:
+            if cache is not None and self.role in ("q", "gate"):
+                r_buf = cache.buffer(m, rank, dev)
+            else:
+                r_buf = self._private_r(m, rank, dev)
+        out = inner.launch(x2d, L=self.A_q, R=self.B_q, r_buf=r_buf, r_mode=mode, alpha=float(self.alpha_svd))
+        if mode == K.R_COMPUTE and cache is not None and self.role in ("q", "gate"):
+            cache.set(r_buf, 2 if self.role == "q" else 1, key)
+        return out.reshape(*lead, inner.out_features)
+
+
+def get_parent_module(model: nn.Module, name: str):
+    parent = model
+    *path, leaf = name.split(".")
+    for part in path:
+        parent = getattr(parent, part)
+    return parent, leaf
+
+
+def _role_from_suffix(sfx: str) -> str:
+    for end, role in (("q_proj", "q"), ("k_proj", "k"), ("v_proj", "v"), ("gate_proj", "gate"), ("up_proj", "up")):
+        if sfx.endswith(end):
+            return role
+    return "solo"
+
+
+def _resolve(bkey: str, module_name: str):
+    """(group key, A key, role, is_group) for one b_ref_map entry.  Grouped entries point at
+    ``<gkey>.B_shared`` and take ``<gkey>.<module suffix>.A``; solo entries point at ``<module>.B`` and take
+    ``<module>.A`` (key scheme written by src/step2_rsvd.py:487-522)."""
+    if "B_shared" in bkey:
+        gkey = bkey.replace(".B_shared", "")
+        suffix = module_name.split(".")[-1]
+        return gkey, f"{gkey}.{suffix}.A", _role_from_suffix(suffix), True
+    gkey = bkey.rsplit(".", 1)[0] if bkey.endswith(".B") else bkey.replace(".B", "")
+    return gkey, gkey + ".A", "solo", False
+
+
+def _patch(model, shared, bmap, alpha_svd, groups_to_patch: Optional[Set[str]], verbose: bool):
+    patched = skipped = 0
+    caches: Dict[str, MiniGroupCache] = {}
+    items = bmap.items()
+    if verbose:
+        items = _tqdm(items, desc="Patching SVD Correction")
+    for weight_name, bkey in items:
+        module_name = weight_name.replace(".weight", "")
+        gkey, a_key, role, is_group = _resolve(bkey, module_name)
+        if groups_to_patch is not None and gkey not in groups_to_patch:
+            continue
+        cache = caches.setdefault(gkey, MiniGroupCache()) if is_group else None
+        A_q, B_q = shared.get(a_key), shared.get(bkey)
+        if A_q is None or B_q is None:
+            skipped += 1
+            continue
+        try:
+            parent, leaf = get_parent_module(model, module_name)
+            inner = getattr(parent, leaf)
+        except (AttributeError, IndexError, KeyError) as exc:
+            if verbose:
+                print(f"AttributeError for {module_name}: {exc}")
+            skipped += 1
+            continue
+        if not isinstance(inner, CudaW4A16Linear):
+            skipped += 1
+            continue
+        dev = inner.qweight_i32.device
+        setattr(parent, leaf, AddSVDCorrection(inner, A_q.to(dev), B_q.to(dev), role=role, is_group=is_group,
+                                               group_cache=cache, alpha_svd=alpha_svd))
+        patched += 1
+    if verbose:
+        print(f"SVD Correction Patching Summary: {patched} patched, {skipped} skipped")
+    return model
+
+
+def patch_svd_correction_wrappers(model, shared, bmap, alpha_svd=1.0):
+    """Wrap every module named in ``bmap`` whose factors exist (src/step3_eval_dataset.py:535-605)."""
+    return _patch(model, shared, bmap, alpha_svd, None, True)
+
+
+def patch_svd_correction_wrappers_cumulative(model, shared, bmap, groups_to_patch: set, alpha_svd=1.0):
+    """GlowQ-S: wrap only modules whose group key (``layer{L}_qkv``, ``layer{L}_mlp`` or a solo module path) is in
+    ``groups_to_patch``; every other module stays a bare CudaW4A16Linear
+    (src/restoration/step4_evaluate_cumulative.py:99-154)."""
+    return _patch(model, shared, bmap, alpha_svd, set(groups_to_patch), False)
+
+
+__all__ = ["AddSVDCorrection", "MiniGroupCache", "patch_svd_correction_wrappers",
+           "patch_svd_correction_wrappers_cumulative", "clear_group_cache", "get_parent_module"]

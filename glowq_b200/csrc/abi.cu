@@ -1,0 +1,407 @@
+// extern "C" entry points declared in include/glowq_w4a16.h: argument validation, launch planning
+// (K slices, workspace layout) and dispatch.  No allocation and no synchronisation on the compute path.
+#include "../../include/glowq_w4a16.h"
+
+#include <algorithm>
+#include <cstring>
+
+#include "params.h"
+
+namespace glowq {
+size_t gemv_smem_bytes(const GemvParams& p, int NT);
+cudaError_t launch_gemv_fused(const GemvParams& p, cudaStream_t stream);
+cudaError_t launch_generic_r(const __half* x, const __half* R, __half* r_buf, float* r32, int r_mode, int M, int IC,
+                             int rank, int x_stride, int R_stride, cudaStream_t stream);
+cudaError_t launch_generic(const __half* x, const MemberDev& mb, const float* r32, int out_fp32, int M, int IC, int rank,
+                           int group_size, int x_stride, cudaStream_t stream);
+cudaError_t launch_dequant(const int32_t* qweight, const __half* scales, const int32_t* qzeros, __half* out, int OC, int IC,
+                           int group_size, int wstride, int zstride, int sstride, cudaStream_t stream);
+bool gemm_supported(const glowq_w4a16_group_t& g);
+size_t gemm_workspace_bytes(int M, int IC, int OC_total, int rank, int n_members);
+int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaError_t* cuda_err);
+}  // namespace glowq
+
+using namespace glowq;
+
+namespace {
+
+thread_local int t_last_cuda_error = 0;
+
+int fail_cuda(cudaError_t e) {
+  t_last_cuda_error = static_cast<int>(e);
+  return GLOWQ_ERR_CUDA;
+}
+
+struct DeviceInfo {
+  bool probed = false;
+  int major = 0;
+  int sms = 0;
+};
+DeviceInfo g_dev[64];
+
+int device_info(const DeviceInfo** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail_cuda(e);
+  if (dev < 0 || dev >= 64) return GLOWQ_ERR_UNSUPPORTED_DEVICE;
+  DeviceInfo& d = g_dev[dev];
+  if (!d.probed) {
+    if ((e = cudaDeviceGetAttribute(&d.major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess) return fail_cuda(e);
+    if ((e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return fail_cuda(e);
+    d.probed = true;
+  }
+  *out = &d;
+  return d.major == 10 ? GLOWQ_OK : GLOWQ_ERR_UNSUPPORTED_DEVICE;
+}
+
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+constexpr int kGemvMaxM = 32;          // tokens per launch of the weight-streaming kernel
+constexpr size_t kXsBudget = 96 * 1024;  // shared-memory bytes for the staged x slice
+
+// K-slice plan of the weight-streaming kernel and the workspace carve-up that goes with it.
+struct GemvPlan {
+  int NT, G, n_tiles, SK, gps, n_r_tiles, SKr, gps_r;
+  size_t off_r_ctr, off_tile_ctr, off_r_partial, off_sk_partial, off_r32, total;
+};
+
+GemvPlan make_plan(int M, int IC, int n_tiles, int rank, int sms, int split_k) {
+  GemvPlan pl{};
+  const int Mc = std::min(M, kGemvMaxM);
+  pl.NT = Mc <= 8 ? 1 : (Mc <= 16 ? 2 : 4);
+  pl.G = ceil_div(IC, kGroup);
+  pl.n_tiles = n_tiles;
+  const int gps_smem = std::max(1, static_cast<int>((kXsBudget / Mc - 64) / 256));
+  int sk = ceil_div(pl.G, gps_smem);
+  if (split_k > 0) {
+    sk = std::max(sk, std::min(split_k, pl.G));
+  } else if (n_tiles < sms) {  // too few row tiles to fill the GPU: slice K, keeping >= 1 group per warp
+    const int want = ceil_div(sms, std::max(1, n_tiles));
+    sk = std::max(sk, std::min(want, std::max(1, pl.G / kGemvWarps)));
+  }
+  pl.gps = ceil_div(pl.G, sk);
+  pl.SK = ceil_div(pl.G, pl.gps);
+  pl.n_r_tiles = ceil_div(std::max(rank, 0), kTileRows);
+  int skr = std::max(ceil_div(pl.G, gps_smem), ceil_div(pl.G, 32));
+  pl.gps_r = ceil_div(pl.G, skr);
+  pl.SKr = ceil_div(pl.G, pl.gps_r);
+  const size_t tile_elems = static_cast<size_t>(pl.NT) * 128;
+  size_t off = kWsHeaderBytes;
+  pl.off_r_ctr = off;
+  off += kMaxRTiles * 4;
+  pl.off_tile_ctr = off;
+  off = align_up(off + static_cast<size_t>(n_tiles) * 4, 256);
+  pl.off_r_partial = off;
+  off = align_up(off + (pl.SKr > 1 ? static_cast<size_t>(pl.n_r_tiles) * pl.SKr * tile_elems * 4 : 0), 256);
+  pl.off_sk_partial = off;
+  off = align_up(off + (pl.SK > 1 ? static_cast<size_t>(n_tiles) * pl.SK * tile_elems * 4 : 0), 256);
+  pl.off_r32 = off;
+  off = align_up(off + static_cast<size_t>(Mc) * std::max(rank, 0) * 4, 256);
+  pl.total = off;
+  return pl;
+}
+
+int validate_member(const glowq_w4a16_member_t& m, int IC, int group_size) {
+  if (!m.qweight || !m.scales || !m.qzeros || !m.out || m.OC <= 0) return GLOWQ_ERR_BAD_ARGUMENT;
+  const int G = ceil_div(IC, group_size);
+  if (m.weight_stride_i32 < ceil_div(IC, 8) || m.scale_stride < G || m.zero_stride_i32 < ceil_div(G, 8))
+    return GLOWQ_ERR_BAD_STRIDE;
+  if (m.out_stride < m.OC) return GLOWQ_ERR_BAD_STRIDE;
+  return GLOWQ_OK;
+}
+
+int validate_group(const glowq_w4a16_group_t& g) {
+  if (!g.x || g.M < 0 || g.IC <= 0 || g.n_members < 1 || g.n_members > GLOWQ_MAX_MEMBERS) return GLOWQ_ERR_BAD_ARGUMENT;
+  if (g.group_size <= 0 || g.group_size % 8 != 0) return GLOWQ_ERR_BAD_GROUP_SIZE;
+  if (g.x_stride < g.IC) return GLOWQ_ERR_BAD_STRIDE;
+  if (g.out_dtype != GLOWQ_OUT_F16 && g.out_dtype != GLOWQ_OUT_F32) return GLOWQ_ERR_BAD_ARGUMENT;
+  if (g.r_mode != GLOWQ_R_NONE && g.r_mode != GLOWQ_R_COMPUTE && g.r_mode != GLOWQ_R_LOAD) return GLOWQ_ERR_BAD_ARGUMENT;
+  if (g.r_mode != GLOWQ_R_NONE) {
+    if (g.rank <= 0 || !g.r_buf) return GLOWQ_ERR_BAD_ARGUMENT;
+    if (g.rank > kMaxRTiles * kTileRows) return GLOWQ_ERR_TOO_LARGE;
+    if (g.r_mode == GLOWQ_R_COMPUTE && (!g.R || g.R_stride < g.IC)) return GLOWQ_ERR_BAD_ARGUMENT;
+  }
+  for (int i = 0; i < g.n_members; ++i) {
+    const int rc = validate_member(g.members[i], g.IC, g.group_size);
+    if (rc != GLOWQ_OK) return rc;
+    if (g.r_mode != GLOWQ_R_NONE && g.members[i].L && g.members[i].L_stride < g.rank) return GLOWQ_ERR_BAD_STRIDE;
+  }
+  if (!g.workspace) return GLOWQ_ERR_BAD_ARGUMENT;
+  return GLOWQ_OK;
+}
+
+// Layouts the streaming kernel takes: group of 128, complete groups physically present in each packed
+// row, 16-byte aligned packed rows / L rows / R rows / r rows.
+bool gemv_fast_ok(const glowq_w4a16_group_t& g) {
+  if (g.group_size != kGroup) return false;
+  const int G = ceil_div(g.IC, kGroup);
+  for (int i = 0; i < g.n_members; ++i) {
+    const auto& m = g.members[i];
+    if (m.weight_stride_i32 < G * 16 || (m.weight_stride_i32 & 3) || !aligned16(m.qweight)) return false;
+    if (g.r_mode != GLOWQ_R_NONE && m.L && (!aligned16(m.L) || (m.L_stride & 7))) return false;
+  }
+  if (g.r_mode != GLOWQ_R_NONE && ((g.rank & 7) || !aligned16(g.r_buf))) return false;
+  if (g.r_mode == GLOWQ_R_COMPUTE && (!aligned16(g.R) || (g.R_stride & 7) || (g.IC & 7))) return false;
+  return true;
+}
+
+int n_tiles_of(const glowq_w4a16_group_t& g) {
+  int n = 0;
+  for (int i = 0; i < g.n_members; ++i) n += ceil_div(g.members[i].OC, kTileRows);
+  return n;
+}
+
+int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cudaStream_t stream) {
+  const bool fast = gemv_fast_ok(g);
+  const int n_tiles = n_tiles_of(g);
+  for (int m0 = 0; m0 < g.M; m0 += kGemvMaxM) {
+    const int Mc = std::min(kGemvMaxM, g.M - m0);
+    const GemvPlan pl = make_plan(Mc, g.IC, n_tiles, g.r_mode != GLOWQ_R_NONE ? g.rank : 0, dev.sms, g.split_k);
+    if (pl.total > g.workspace_bytes) return GLOWQ_ERR_WORKSPACE_TOO_SMALL;
+    unsigned char* ws = static_cast<unsigned char*>(g.workspace);
+    const __half* x = static_cast<const __half*>(g.x) + static_cast<size_t>(m0) * g.x_stride;
+    __half* r_buf = g.r_buf ? static_cast<__half*>(g.r_buf) + static_cast<size_t>(m0) * g.rank : nullptr;
+    const int esz = g.out_dtype == GLOWQ_OUT_F32 ? 4 : 2;
+
+    GemvParams p{};
+    p.x = x;
+    p.R = static_cast<const __half*>(g.R);
+    p.r_buf = r_buf;
+    p.ws_head = reinterpret_cast<uint32_t*>(ws);
+    p.r_tile_ctr = reinterpret_cast<uint32_t*>(ws + pl.off_r_ctr);
+    p.tile_ctr = reinterpret_cast<uint32_t*>(ws + pl.off_tile_ctr);
+    p.r_partial = reinterpret_cast<float*>(ws + pl.off_r_partial);
+    p.sk_partial = reinterpret_cast<float*>(ws + pl.off_sk_partial);
+    p.M = Mc;
+    p.IC = g.IC;
+    p.x_stride = g.x_stride;
+    p.R_stride = g.R_stride;
+    p.G = pl.G;
+    p.rank = g.r_mode != GLOWQ_R_NONE ? g.rank : 0;
+    p.r_mode = g.r_mode;
+    p.out_fp32 = g.out_dtype == GLOWQ_OUT_F32;
+    p.n_members = g.n_members;
+    p.n_tiles = n_tiles;
+    p.SK = pl.SK;
+    p.gps = pl.gps;
+    p.n_r_tiles = pl.n_r_tiles;
+    p.SKr = pl.SKr;
+    p.gps_r = pl.gps_r;
+    p.n_r_units = g.r_mode == GLOWQ_R_COMPUTE ? pl.n_r_tiles * pl.SKr : 0;
+    p.x_vec_ok = aligned16(x) && (g.x_stride % 8 == 0);
+    p.xs_stride = std::max(pl.gps, g.r_mode == GLOWQ_R_COMPUTE ? pl.gps_r : 0) * 256 + 64;
+    int tb = 0;
+    bool any_corr = false;
+    for (int i = 0; i < g.n_members; ++i) {
+      const auto& m = g.members[i];
+      MemberDev& d = p.mem[i];
+      d.qweight = m.qweight;
+      d.scales = static_cast<const __half*>(m.scales);
+      d.qzeros = m.qzeros;
+      d.bias = static_cast<const __half*>(m.bias);
+      d.L = g.r_mode != GLOWQ_R_NONE ? static_cast<const __half*>(m.L) : nullptr;
+      d.out = static_cast<unsigned char*>(m.out) + static_cast<size_t>(m0) * m.out_stride * esz;
+      d.OC = m.OC;
+      d.wstride = m.weight_stride_i32;
+      d.zstride = m.zero_stride_i32;
+      d.sstride = m.scale_stride;
+      d.Lstride = m.L_stride;
+      d.out_stride = m.out_stride;
+      d.alpha = m.alpha;
+      d.tile_begin = tb;
+      tb += ceil_div(m.OC, kTileRows);
+      any_corr = any_corr || (d.L != nullptr && d.alpha != 0.f);
+    }
+    if (p.r_mode != GLOWQ_R_NONE && !any_corr && p.r_mode == GLOWQ_R_LOAD) p.r_mode = GLOWQ_R_NONE;
+
+    cudaError_t e;
+    if (fast) {
+      if (gemv_smem_bytes(p, pl.NT) > 200 * 1024) return GLOWQ_ERR_UNSUPPORTED_SHAPE;
+      e = launch_gemv_fused(p, stream);
+      if (e != cudaSuccess) return fail_cuda(e);
+    } else {
+      float* r32 = nullptr;
+      if (p.r_mode != GLOWQ_R_NONE) {
+        r32 = reinterpret_cast<float*>(ws + pl.off_r32);
+        e = launch_generic_r(x, p.R, r_buf, r32, p.r_mode, Mc, g.IC, p.rank, g.x_stride, g.R_stride, stream);
+        if (e != cudaSuccess) return fail_cuda(e);
+      }
+      for (int i = 0; i < g.n_members; ++i) {
+        e = launch_generic(x, p.mem[i], r32, p.out_fp32, Mc, g.IC, p.rank, g.group_size, g.x_stride, stream);
+        if (e != cudaSuccess) return fail_cuda(e);
+      }
+    }
+  }
+  return GLOWQ_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int glowq_w4a16_version(void) { return GLOWQ_W4A16_ABI_VERSION; }
+
+const char* glowq_w4a16_strerror(int status) {
+  switch (status) {
+    case GLOWQ_OK: return "ok";
+    case GLOWQ_ERR_BAD_ARGUMENT: return "bad argument (null pointer, size, or rank/mode mismatch)";
+    case GLOWQ_ERR_BAD_GROUP_SIZE: return "group_size must be > 0 and a multiple of 8";
+    case GLOWQ_ERR_BAD_STRIDE: return "packed columns / scales / zero words / output stride too small";
+    case GLOWQ_ERR_WORKSPACE_TOO_SMALL: return "workspace too small (see glowq_w4a16_workspace_bytes)";
+    case GLOWQ_ERR_UNSUPPORTED_DEVICE: return "unsupported device: this library runs on sm_100 (B200) only; there is no fallback";
+    case GLOWQ_ERR_CUDA: return "CUDA runtime error (see glowq_w4a16_last_cuda_error)";
+    case GLOWQ_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
+    case GLOWQ_ERR_UNSUPPORTED_SHAPE: return "unsupported shape";
+    case GLOWQ_ERR_TOO_LARGE: return "size beyond the supported maximum";
+    default: return "unknown status";
+  }
+}
+
+int glowq_w4a16_last_cuda_error(void) { return t_last_cuda_error; }
+
+int glowq_w4a16_dequant(const int32_t* qweight, const void* scales, const int32_t* qzeros, void* out_w, int OC, int IC,
+                        int group_size, int weight_stride_i32, int zero_stride_i32, int scale_stride, void* stream) {
+  if (!qweight || !scales || !qzeros || !out_w || OC <= 0 || IC <= 0) return GLOWQ_ERR_BAD_ARGUMENT;
+  if (group_size <= 0 || group_size % 8 != 0) return GLOWQ_ERR_BAD_GROUP_SIZE;
+  const int G = ceil_div(IC, group_size);
+  if (weight_stride_i32 < ceil_div(IC, 8) || scale_stride < G || zero_stride_i32 < ceil_div(G, 8)) return GLOWQ_ERR_BAD_STRIDE;
+  const DeviceInfo* dev = nullptr;
+  int rc = device_info(&dev);
+  if (rc != GLOWQ_OK) return rc;
+  cudaError_t e = launch_dequant(qweight, static_cast<const __half*>(scales), qzeros, static_cast<__half*>(out_w), OC, IC,
+                                 group_size, weight_stride_i32, zero_stride_i32, scale_stride,
+                                 static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? GLOWQ_OK : fail_cuda(e);
+}
+
+size_t glowq_w4a16_workspace_bytes(int M, int IC, int OC_total, int rank, int n_members) {
+  if (M <= 0 || IC <= 0 || OC_total <= 0) return kWsHeaderBytes;
+  n_members = std::max(1, std::min(n_members, GLOWQ_MAX_MEMBERS));
+  const int n_tiles = ceil_div(OC_total, kTileRows) + n_members;
+  // planned for more SMs than any device has, which bounds the split-K partial-sum area from above
+  const GemvPlan pl = make_plan(M, IC, n_tiles, rank, 1024, 0);
+  size_t need = pl.total;
+  need = std::max(need, gemm_workspace_bytes(M, IC, OC_total, rank, n_members));
+  return align_up(need, 256);
+}
+
+int glowq_w4a16_group_forward(const glowq_w4a16_group_t* group) {
+  if (!group) return GLOWQ_ERR_BAD_ARGUMENT;
+  const glowq_w4a16_group_t& g = *group;
+  int rc = validate_group(g);
+  if (rc != GLOWQ_OK) return rc;
+  const DeviceInfo* dev = nullptr;
+  rc = device_info(&dev);
+  if (rc != GLOWQ_OK) return rc;
+  if (g.M == 0) return GLOWQ_OK;
+  cudaStream_t stream = static_cast<cudaStream_t>(g.stream);
+  bool use_gemm = g.kernel == GLOWQ_KERNEL_GEMM || (g.kernel == GLOWQ_KERNEL_AUTO && g.M > kGemvMaxM);
+  if (use_gemm && gemm_supported(g)) {
+    cudaError_t ce = cudaSuccess;
+    rc = gemm_group_forward(g, stream, &ce);
+    if (rc == GLOWQ_ERR_CUDA) return fail_cuda(ce);
+    return rc;
+  }
+  return gemv_group_forward(g, *dev, stream);
+}
+
+int glowq_w4a16_group_forward_many(const glowq_w4a16_group_t* groups, int n) {
+  if (!groups || n < 0) return GLOWQ_ERR_BAD_ARGUMENT;
+  for (int i = 0; i < n; ++i) {
+    const int rc = glowq_w4a16_group_forward(groups + i);
+    if (rc != GLOWQ_OK) return rc;
+  }
+  return GLOWQ_OK;
+}
+
+static void fill_plain(glowq_w4a16_group_t& g, const void* x, const int32_t* qweight, const void* scales,
+                       const int32_t* qzeros, void* out, int M, int IC, int OC, int group_size, int wstride, int zstride,
+                       int sstride, void* workspace, size_t workspace_bytes, void* stream) {
+  std::memset(&g, 0, sizeof(g));
+  g.x = x;
+  g.workspace = workspace;
+  g.workspace_bytes = workspace_bytes;
+  g.stream = stream;
+  g.M = M;
+  g.IC = IC;
+  g.x_stride = IC;
+  g.group_size = group_size;
+  g.r_mode = GLOWQ_R_NONE;
+  g.out_dtype = GLOWQ_OUT_F16;
+  g.n_members = 1;
+  g.members[0].qweight = qweight;
+  g.members[0].scales = scales;
+  g.members[0].qzeros = qzeros;
+  g.members[0].out = out;
+  g.members[0].OC = OC;
+  g.members[0].weight_stride_i32 = wstride;
+  g.members[0].zero_stride_i32 = zstride;
+  g.members[0].scale_stride = sstride;
+  g.members[0].out_stride = OC;
+}
+
+int glowq_w4a16_gemv_forward(const void* x, const int32_t* qweight, const void* scales, const int32_t* qzeros, void* out,
+                             int M, int IC, int OC, int group_size, int weight_stride_i32, int zero_stride_i32,
+                             int scale_stride, void* workspace, size_t workspace_bytes, void* stream) {
+  glowq_w4a16_group_t g;
+  fill_plain(g, x, qweight, scales, qzeros, out, M, IC, OC, group_size, weight_stride_i32, zero_stride_i32, scale_stride,
+             workspace, workspace_bytes, stream);
+  g.kernel = GLOWQ_KERNEL_GEMV;
+  return glowq_w4a16_group_forward(&g);
+}
+
+int glowq_w4a16_gemm_forward(const void* x, const int32_t* qweight, const void* scales, const int32_t* qzeros, void* out,
+                             int M, int IC, int OC, int group_size, int split_k_iters, int weight_stride_i32,
+                             int zero_stride_i32, int scale_stride, void* workspace, size_t workspace_bytes, void* stream) {
+  (void)split_k_iters;
+  glowq_w4a16_group_t g;
+  fill_plain(g, x, qweight, scales, qzeros, out, M, IC, OC, group_size, weight_stride_i32, zero_stride_i32, scale_stride,
+             workspace, workspace_bytes, stream);
+  g.kernel = GLOWQ_KERNEL_GEMM;
+  return glowq_w4a16_group_forward(&g);
+}
+
+int glowq_w4a16_group_forward_host(const glowq_w4a16_group_t* group, const void* x_host, void* const* out_host) {
+  if (!group || !x_host || !out_host) return GLOWQ_ERR_BAD_ARGUMENT;
+  const glowq_w4a16_group_t& g = *group;
+  int rc = validate_group(g);
+  if (rc != GLOWQ_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(g.stream);
+  cudaError_t e;
+  if (g.M > 0) {
+    e = cudaMemcpy2DAsync(const_cast<void*>(g.x), static_cast<size_t>(g.x_stride) * 2, x_host, static_cast<size_t>(g.IC) * 2,
+                          static_cast<size_t>(g.IC) * 2, g.M, cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return fail_cuda(e);
+  }
+  rc = glowq_w4a16_group_forward(group);
+  if (rc != GLOWQ_OK) return rc;
+  const size_t esz = g.out_dtype == GLOWQ_OUT_F32 ? 4 : 2;
+  for (int i = 0; i < g.n_members && g.M > 0; ++i) {
+    const auto& m = g.members[i];
+    if (!out_host[i]) return GLOWQ_ERR_BAD_ARGUMENT;
+    e = cudaMemcpy2DAsync(out_host[i], m.OC * esz, m.out, m.out_stride * esz, m.OC * esz, g.M, cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) return fail_cuda(e);
+  }
+  e = cudaStreamSynchronize(stream);
+  return e == cudaSuccess ? GLOWQ_OK : fail_cuda(e);
+}
+
+int glowq_w4a16_read_status(void* workspace, void* stream) {
+  if (!workspace) return GLOWQ_ERR_BAD_ARGUMENT;
+  uint32_t host = 0;
+  uint32_t* word = static_cast<uint32_t*>(workspace) + WS_STATUS;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(&host, word, 4, cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return fail_cuda(e);
+  if (host != 0) {
+    e = cudaMemsetAsync(word, 0, 4, s);
+    if (e != cudaSuccess) return fail_cuda(e);
+    return GLOWQ_ERR_DEVICE_TIMEOUT;
+  }
+  return GLOWQ_OK;
+}
+
+}  // extern "C"

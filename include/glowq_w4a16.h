@@ -1,0 +1,161 @@
+/*
+ * glowq_w4a16.h - C ABI of the B200 (sm_100a) corrected W4A16 linear
+ *
+ *     y_i = dequant(Q_i) . x  +  alpha * L_i . (R_g . x)  (+ bias_i)
+ *
+ * Q_i: int4 codes, 8 per int32 (nibble j of word w = input column 8w+j), asymmetric, one fp16
+ * scale and one 4-bit zero-point per (output row, group of `group_size` input columns); zero-points
+ * are packed 8 per int32 the same way.  This is GlowQ's CudaW4A16Linear buffer layout
+ * (src/cuda_w4a16/linear.py:42-46, 75-88, 104-106) and is consumed unchanged.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless the name ends in _host;
+ *   - fp16 data are passed as `const void*` (IEEE binary16 bits);
+ *   - the caller owns all memory, including outputs, the r cache and the workspace; nothing here
+ *     allocates per call (the reference allocates its output and a full fp16 weight temporary per call:
+ *     csrc/gemv_w4a16.cu:187, csrc/gemm_w4a16.cu:106);
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it and no call synchronises
+ *     except the *_host variant and glowq_w4a16_read_status;
+ *   - every function returns GLOWQ_OK or a GLOWQ_ERR_* code and never throws or aborts; the
+ *     reference reports the same conditions through TORCH_CHECK (csrc/gemv_w4a16.cu:152-185);
+ *   - there is no CPU fallback: on a device that is not compute capability 10.x every compute entry
+ *     point returns GLOWQ_ERR_UNSUPPORTED_DEVICE.
+ */
+#ifndef GLOWQ_W4A16_H_
+#define GLOWQ_W4A16_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GLOWQ_W4A16_ABI_VERSION 1
+
+enum {
+  GLOWQ_OK = 0,
+  GLOWQ_ERR_BAD_ARGUMENT = 1,       /* null pointer, non-positive size, rank/mode mismatch          */
+  GLOWQ_ERR_BAD_GROUP_SIZE = 2,     /* group_size <= 0 or not a multiple of 8                        */
+  GLOWQ_ERR_BAD_STRIDE = 3,         /* packed columns / scales / zero words too few for IC           */
+  GLOWQ_ERR_WORKSPACE_TOO_SMALL = 4,
+  GLOWQ_ERR_UNSUPPORTED_DEVICE = 5, /* not an sm_100-class GPU                                       */
+  GLOWQ_ERR_CUDA = 6,               /* a CUDA runtime call failed; see glowq_w4a16_last_cuda_error   */
+  GLOWQ_ERR_DEVICE_TIMEOUT = 7,     /* a bounded device-side wait ran out (read from the status word) */
+  GLOWQ_ERR_UNSUPPORTED_SHAPE = 8,
+  GLOWQ_ERR_TOO_LARGE = 9
+};
+
+enum { GLOWQ_OUT_F16 = 0, GLOWQ_OUT_F32 = 1 };
+
+/* What a launch does about the shared right-factor product r = R_g . x  (the device-side analogue of
+ * MiniGroupCache: src/step3_eval_dataset.py:417-444 and the role logic at :481-504). */
+enum {
+  GLOWQ_R_NONE = 0,    /* plain W4A16 (no wrapper, alpha == 0, or a GlowQ-S group that is switched off) */
+  GLOWQ_R_COMPUTE = 1, /* roles q / gate / solo: compute r in this launch and leave it in r_buf           */
+  GLOWQ_R_LOAD = 2     /* roles k / v / up on a cache hit: r_buf already holds r for this x               */
+};
+
+enum { GLOWQ_KERNEL_AUTO = 0, GLOWQ_KERNEL_GEMV = 1, GLOWQ_KERNEL_GEMM = 2 };
+
+#define GLOWQ_MAX_MEMBERS 4
+
+/* One quantised linear of a group (q_proj, k_proj, ... ). */
+typedef struct glowq_w4a16_member {
+  const int32_t* qweight; /* [OC, weight_stride_i32]                                          */
+  const void* scales;     /* fp16 [OC, scale_stride]                                          */
+  const int32_t* qzeros;  /* [OC, zero_stride_i32]                                            */
+  const void* bias;       /* fp16 [OC] or NULL                                                */
+  const void* L;          /* fp16 [OC, L_stride] left factor (A_q) or NULL = no correction    */
+  void* out;              /* [M, out_stride] fp16 or fp32                                     */
+  int32_t OC;
+  int32_t weight_stride_i32;
+  int32_t zero_stride_i32;
+  int32_t scale_stride;
+  int32_t L_stride;
+  int32_t out_stride;
+  float alpha;            /* alpha_svd of this member (step3_eval_dataset.py:511)             */
+  int32_t reserved;
+} glowq_w4a16_member_t;
+
+/* A group of 1..4 linears that consume the same x and share one right factor R_g. */
+typedef struct glowq_w4a16_group {
+  const void* x;          /* fp16 [M, x_stride]                                               */
+  const void* R;          /* fp16 [rank, R_stride] (B_q); used when r_mode == GLOWQ_R_COMPUTE */
+  void* r_buf;            /* fp16 [M, rank]: r = R.x, written (COMPUTE) or read (LOAD)        */
+  void* workspace;        /* >= glowq_w4a16_workspace_bytes(); zero it once after allocation  */
+  size_t workspace_bytes;
+  void* stream;           /* cudaStream_t                                                     */
+  int32_t M;
+  int32_t IC;
+  int32_t x_stride;
+  int32_t R_stride;
+  int32_t rank;           /* 0 with GLOWQ_R_NONE                                              */
+  int32_t group_size;
+  int32_t r_mode;
+  int32_t out_dtype;      /* GLOWQ_OUT_F16 / GLOWQ_OUT_F32 (W4A16_KERNEL_OUT_DTYPE)           */
+  int32_t kernel;         /* GLOWQ_KERNEL_AUTO picks the GEMV for M <= 32, the GEMM above     */
+  int32_t n_members;
+  int32_t split_k;        /* 0 = choose; >0 forces the number of K slices of the GEMV         */
+  int32_t reserved;
+  glowq_w4a16_member_t members[GLOWQ_MAX_MEMBERS];
+} glowq_w4a16_group_t;
+
+/* ABI version of the loaded library (compare with GLOWQ_W4A16_ABI_VERSION). */
+int glowq_w4a16_version(void);
+
+/* Static text for a status code. */
+const char* glowq_w4a16_strerror(int status);
+
+/* cudaError_t of the most recent failing CUDA call on this thread (0 if none). */
+int glowq_w4a16_last_cuda_error(void);
+
+/* Dequantise a whole weight: out_w[OC, IC] fp16 = half_rn((code - zero) * scale).
+ * Replaces dequant_w4a16_asym_i32_kernel (csrc/gemm_w4a16.cu:19-50); bit-exact with it and with
+ * CudaW4A16Linear._dequant_chunk (src/cuda_w4a16/linear.py:248-253). */
+int glowq_w4a16_dequant(const int32_t* qweight, const void* scales, const int32_t* qzeros, void* out_w,
+                        int OC, int IC, int group_size, int weight_stride_i32, int zero_stride_i32,
+                        int scale_stride, void* stream);
+
+/* Plain W4A16 product out[M, OC] (fp16) = x[M, IC] . dequant(Q)^T with the weight-streaming kernel.
+ * Replaces w4a16_gemv_forward_cuda / gemv_w4a16_asym (csrc/gemv_w4a16.cu:146-214, csrc/pybind.cpp:19-34).
+ * The caller allocates `out`; `workspace` as for a group call. */
+int glowq_w4a16_gemv_forward(const void* x, const int32_t* qweight, const void* scales, const int32_t* qzeros,
+                             void* out, int M, int IC, int OC, int group_size, int weight_stride_i32,
+                             int zero_stride_i32, int scale_stride, void* workspace, size_t workspace_bytes,
+                             void* stream);
+
+/* Same product with the tensor-core kernel.  Replaces w4a16_gemm_forward_cuda
+ * (csrc/gemm_w4a16.cu:76-135); `split_k_iters` is accepted and ignored as there (:83). */
+int glowq_w4a16_gemm_forward(const void* x, const int32_t* qweight, const void* scales, const int32_t* qzeros,
+                             void* out, int M, int IC, int OC, int group_size, int split_k_iters,
+                             int weight_stride_i32, int zero_stride_i32, int scale_stride, void* workspace,
+                             size_t workspace_bytes, void* stream);
+
+/* The corrected linear for a whole group in one launch.  Replaces, per member, the sequence
+ * CudaW4A16Linear.forward (src/cuda_w4a16/linear.py:155-187) -> F.linear(x, B_q) or cache hit ->
+ * F.linear(r, A_q) -> z.add_(.., alpha) of AddSVDCorrection.forward (src/step3_eval_dataset.py:470-511). */
+int glowq_w4a16_group_forward(const glowq_w4a16_group_t* group);
+
+/* `n` group calls issued back to back on their streams, in array order (one C call for a whole token step:
+ * the reference pays one Python dispatch per module, src/cuda_w4a16/linear.py:155-187).  Stops at and
+ * returns the first failing status. */
+int glowq_w4a16_group_forward_many(const glowq_w4a16_group_t* groups, int n);
+
+/* Same call with HOST activations: copies x_host[M, IC] (fp16, dense) to group->x, runs the group,
+ * copies each member's output to out_host[i] (dense [M, OC_i] in out_dtype) and synchronises the stream.
+ * Weights, factors, r_buf and workspace stay device-resident, as the reference keeps them after .to(device)
+ * (src/step3_eval_dataset.py:1047-1050). */
+int glowq_w4a16_group_forward_host(const glowq_w4a16_group_t* group, const void* x_host, void* const* out_host);
+
+/* Bytes of workspace a group call with these sizes needs (sync words + split-K partial sums). */
+size_t glowq_w4a16_workspace_bytes(int M, int IC, int OC_total, int rank, int n_members);
+
+/* Copy the device status word of a workspace to the host (synchronises `stream`) and clear it.
+ * Returns GLOWQ_OK or GLOWQ_ERR_DEVICE_TIMEOUT. */
+int glowq_w4a16_read_status(void* workspace, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GLOWQ_W4A16_H_ */

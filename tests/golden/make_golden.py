@@ -115,11 +115,14 @@ def forward_cases():
 
 
 # ---------------------------------------------------------------- 3. conversion pass + patchers
+WRAPPER_TYPES = [s3.AddSVDCorrection]   # the GlowQ-S script brings its own copy of the class
+
+
 def describe(model):
     rows = {}
     caches = {}
     for name, mod in model.named_modules():
-        if isinstance(mod, s3.AddSVDCorrection):
+        if isinstance(mod, tuple(WRAPPER_TYPES)):
             cid = None
             if mod.group_cache is not None:
                 cid = caches.setdefault(id(mod.group_cache), len(caches))
@@ -138,6 +141,7 @@ def patch_cases():
     os.environ.pop("DISABLE_TRITON", None)   # its TritonTrue4BitLinear class needs the triton import
     import step4_evaluate_cumulative as s4
     os.environ["DISABLE_TRITON"] = "1"
+    WRAPPER_TYPES.append(s4.AddSVDCorrection)
 
     result = {}
     model = convert_to_cuda_w4a16(ToyDecoder(), 128)
