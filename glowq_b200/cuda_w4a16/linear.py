@@ -139,10 +139,10 @@ class CudaW4A16Linear(nn.Module):
         return K.KERNEL_AUTO
 
     def _flatten_input(self, x: torch.Tensor):
-        if not x.is_cuda:
-            raise RuntimeError("CudaW4A16Linear runs on CUDA (sm_100) tensors only; there is no CPU path")
         if x.shape[-1] != self.in_features:
             raise ValueError(f"Input dim mismatch: got {x.shape[-1]}, expected {self.in_features}")
+        if not x.is_cuda:
+            raise RuntimeError("CudaW4A16Linear runs on CUDA (sm_100) tensors only; there is no CPU path")
         x2d = x.reshape(-1, x.shape[-1])
         if x2d.dtype != torch.float16:
             x2d = x2d.to(torch.float16)

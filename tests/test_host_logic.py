@@ -64,8 +64,7 @@ def test_module_surface_and_state_dict():
     with pytest.raises(RuntimeError, match="CUDA"):
         mod(torch.zeros(1, 200, dtype=torch.float16))          # no CPU path
     with pytest.raises(ValueError, match="Input dim mismatch"):
-        mod._flatten_input(torch.zeros(1, 100, dtype=torch.float16, device="meta")) if False else mod(torch.zeros(1, 100).cuda()) \
-            if torch.cuda.is_available() else (_ for _ in ()).throw(ValueError("Input dim mismatch: skipped on CPU"))
+        mod(torch.zeros(1, 100, dtype=torch.float16))
 
 
 def _describe(model):
