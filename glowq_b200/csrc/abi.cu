@@ -3,13 +3,15 @@
 #include "../../include/glowq_w4a16.h"
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "params.h"
 
 namespace glowq {
 size_t gemv_smem_bytes(const GemvParams& p, int NT);
-cudaError_t launch_gemv_fused(const GemvParams& p, cudaStream_t stream);
+cudaError_t launch_gemv_stream(const GemvParams& p, const TensorMaps& tm, int NT, int grid, cudaStream_t stream);
 cudaError_t launch_generic_r(const __half* x, const __half* R, __half* r_buf, float* r32, int r_mode, int M, int IC,
                              int rank, int x_stride, int R_stride, cudaStream_t stream);
 cudaError_t launch_generic(const __half* x, const MemberDev& mb, const float* r32, int out_fp32, int M, int IC, int rank,
@@ -54,40 +56,140 @@ int device_info(const DeviceInfo** out) {
   return d.major == 10 ? GLOWQ_OK : GLOWQ_ERR_UNSUPPORTED_DEVICE;
 }
 
+// ---------------------------------------------------------------- TMA descriptors
+// cuTensorMapEncodeTiled is fetched from the driver at run time (no link-time dependency on libcuda), and encoded
+// descriptors are kept in a small direct-mapped cache keyed by (address, shape, box): a decode loop that is not
+// graph-captured re-uses them instead of re-encoding seven descriptors per layer per token.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  uint64_t dim0, dim1, stride_bytes;
+  uint32_t box0, box1, dtype;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && dim0 == o.dim0 && dim1 == o.dim1 && stride_bytes == o.stride_bytes && box0 == o.box0 &&
+           box1 == o.box1 && dtype == o.dtype;
+  }
+};
+struct MapSlot {
+  MapKey key{};
+  bool valid = false;
+  alignas(64) CUtensorMap map;
+};
+constexpr int kMapCacheSlots = 4096;
+MapSlot g_map_cache[kMapCacheSlots];
+std::mutex g_map_mutex;
+
+// Row-major 2-D tensor [dim1 rows, dim0 elements], row pitch stride_bytes, box [box1 rows, box0 elements].
+int tensor_map_2d(CUtensorMap* out, CUtensorMapDataType dtype, const void* ptr, uint64_t dim0, uint64_t dim1,
+                  uint64_t stride_bytes, uint32_t box0, uint32_t box1) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return GLOWQ_ERR_UNSUPPORTED_DEVICE;
+  const MapKey key{ptr, dim0, dim1, stride_bytes, box0, box1, static_cast<uint32_t>(dtype)};
+  size_t h = reinterpret_cast<uintptr_t>(ptr) >> 8;
+  h = (h ^ (h >> 12) ^ (dim0 * 0x9E3779B97F4A7C15ull) ^ (dim1 << 7) ^ box0) % kMapCacheSlots;
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  MapSlot& slot = g_map_cache[h];
+  if (!(slot.valid && slot.key == key)) {
+    const cuuint64_t dims[2] = {dim0, dim1};
+    const cuuint64_t strides[1] = {stride_bytes};
+    const cuuint32_t box[2] = {box0, box1};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(&slot.map, dtype, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      slot.valid = false;
+      return GLOWQ_ERR_CUDA;
+    }
+    slot.key = key;
+    slot.valid = true;
+  }
+  std::memcpy(out, &slot.map, sizeof(CUtensorMap));
+  return GLOWQ_OK;
+}
+
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-constexpr int kGemvMaxM = 32;          // tokens per launch of the weight-streaming kernel
-constexpr size_t kXsBudget = 96 * 1024;  // shared-memory bytes for the staged x slice
+constexpr int kGemvMaxM = 32;                 // tokens per launch of the weight-streaming kernel
+constexpr size_t kSmemTwoPerSm = 112 * 1024;  // dynamic shared memory that still lets two CTAs share an SM
+constexpr size_t kSmemOnePerSm = 224 * 1024;
 
-// K-slice plan of the weight-streaming kernel and the workspace carve-up that goes with it.
+int env_int(const char* name, int dflt) {
+  const char* v = std::getenv(name);
+  return (v && *v) ? std::atoi(v) : dflt;
+}
+
+// Launch plan of the weight-streaming kernel (K slices, pipeline depth, grid) and the workspace carve-up.
 struct GemvPlan {
-  int NT, G, n_tiles, SK, gps, n_r_tiles, SKr, gps_r;
+  int NT, G, n_tiles, SK, gps, n_r_tiles, SKr, stages, ctas_per_sm, meta_gp, meta_gw, xs_stride;
+  size_t smem;
   size_t off_r_ctr, off_tile_ctr, off_r_partial, off_sk_partial, off_r32, total;
 };
 
+size_t plan_smem(const GemvPlan& pl, int Mc, int stages) {
+  return 256 + static_cast<size_t>(stages) * kStageBytes +
+         static_cast<size_t>(kMetaDepth) * kTileRows * (pl.meta_gp * 2 + pl.meta_gw * 4) +
+         static_cast<size_t>(kConsumerWarps + 1) * kRowTiles * pl.NT * 512 + static_cast<size_t>(pl.gps) * pl.NT * 32 +
+         static_cast<size_t>(Mc) * pl.xs_stride;
+}
+
 GemvPlan make_plan(int M, int IC, int n_tiles, int rank, int sms, int split_k) {
+  static const int forced_stages = env_int("GLOWQ_GEMV_STAGES", 0);       // tuning overrides
+  static const int forced_ctas = env_int("GLOWQ_GEMV_CTAS_PER_SM", 0);
   GemvPlan pl{};
   const int Mc = std::min(M, kGemvMaxM);
   pl.NT = Mc <= 8 ? 1 : (Mc <= 16 ? 2 : 4);
   pl.G = ceil_div(IC, kGroup);
   pl.n_tiles = n_tiles;
-  const int gps_smem = std::max(1, static_cast<int>((kXsBudget / Mc - 64) / 256));
-  int sk = ceil_div(pl.G, gps_smem);
+  const int chunks = ceil_div(pl.G, kChunkGroups);
+  int sk = 1;
   if (split_k > 0) {
-    sk = std::max(sk, std::min(split_k, pl.G));
-  } else if (n_tiles < sms) {  // too few row tiles to fill the GPU: slice K, keeping >= 1 group per warp
-    const int want = ceil_div(sms, std::max(1, n_tiles));
-    sk = std::max(sk, std::min(want, std::max(1, pl.G / kGemvWarps)));
+    sk = std::min(split_k, chunks);
+  } else if (n_tiles < sms) {  // too few row tiles to give every SM one: slice K as well
+    sk = std::min(ceil_div(sms, std::max(1, n_tiles)), chunks);
   }
-  pl.gps = ceil_div(pl.G, sk);
-  pl.SK = ceil_div(pl.G, pl.gps);
-  pl.n_r_tiles = ceil_div(std::max(rank, 0), kTileRows);
-  int skr = std::max(ceil_div(pl.G, gps_smem), ceil_div(pl.G, 32));
-  pl.gps_r = ceil_div(pl.G, skr);
-  pl.SKr = ceil_div(pl.G, pl.gps_r);
-  const size_t tile_elems = static_cast<size_t>(pl.NT) * 128;
+  for (;; ++sk) {
+    pl.gps = ceil_div(chunks, sk) * kChunkGroups;   // whole pipeline stages per slice
+    pl.SK = ceil_div(pl.G, pl.gps);
+    pl.meta_gp = (std::min(pl.gps, pl.G) + 1) & ~1;
+    pl.meta_gw = ceil_div(pl.gps, 8);
+    pl.xs_stride = pl.gps * 256 + 64;
+    // deepest ring that fits, preferring two CTAs per SM (16 consumer warps per SM) when that leaves >= 4 stages
+    pl.ctas_per_sm = (pl.NT <= 2) ? 2 : 1;
+    if (forced_ctas > 0) pl.ctas_per_sm = std::min(forced_ctas, pl.ctas_per_sm);
+    pl.stages = 0;
+    for (int cps = pl.ctas_per_sm; cps >= 1 && pl.stages == 0; --cps) {
+      const size_t cap = cps == 2 ? kSmemTwoPerSm : kSmemOnePerSm;
+      for (int st = kMaxStages; st >= (cps == 2 ? 3 : 2); --st)
+        if (plan_smem(pl, Mc, st) <= cap) {
+          pl.stages = st;
+          pl.ctas_per_sm = cps;
+          break;
+        }
+    }
+    if (pl.stages > 0 || pl.gps == kChunkGroups) break;  // fits, or K cannot be sliced any finer
+  }
+  if (forced_stages > 0 && pl.stages > 0) pl.stages = std::max(2, std::min(forced_stages, pl.stages));
+  pl.smem = plan_smem(pl, Mc, pl.stages);
+  pl.n_r_tiles = ceil_div(std::max(rank, 0), kRTileRows);
+  pl.SKr = chunks;
+  const size_t tile_elems = static_cast<size_t>(kRowTiles) * pl.NT * 128;
   size_t off = kWsHeaderBytes;
   pl.off_r_ctr = off;
   off += kMaxRTiles * 4;
@@ -113,6 +215,7 @@ int validate_member(const glowq_w4a16_member_t& m, int IC, int group_size) {
 }
 
 int validate_group(const glowq_w4a16_group_t& g) {
+  if (g.M == 0 && g.IC > 0 && g.n_members >= 1 && g.n_members <= GLOWQ_MAX_MEMBERS) return GLOWQ_OK;  // empty batch
   if (!g.x || g.M < 0 || g.IC <= 0 || g.n_members < 1 || g.n_members > GLOWQ_MAX_MEMBERS) return GLOWQ_ERR_BAD_ARGUMENT;
   if (g.group_size <= 0 || g.group_size % 8 != 0) return GLOWQ_ERR_BAD_GROUP_SIZE;
   if (g.x_stride < g.IC) return GLOWQ_ERR_BAD_STRIDE;
@@ -120,7 +223,7 @@ int validate_group(const glowq_w4a16_group_t& g) {
   if (g.r_mode != GLOWQ_R_NONE && g.r_mode != GLOWQ_R_COMPUTE && g.r_mode != GLOWQ_R_LOAD) return GLOWQ_ERR_BAD_ARGUMENT;
   if (g.r_mode != GLOWQ_R_NONE) {
     if (g.rank <= 0 || !g.r_buf) return GLOWQ_ERR_BAD_ARGUMENT;
-    if (g.rank > kMaxRTiles * kTileRows) return GLOWQ_ERR_TOO_LARGE;
+    if (g.rank > kMaxRTiles * kRTileRows) return GLOWQ_ERR_TOO_LARGE;
     if (g.r_mode == GLOWQ_R_COMPUTE && (!g.R || g.R_stride < g.IC)) return GLOWQ_ERR_BAD_ARGUMENT;
   }
   for (int i = 0; i < g.n_members; ++i) {
@@ -188,10 +291,13 @@ int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cuda
     p.gps = pl.gps;
     p.n_r_tiles = pl.n_r_tiles;
     p.SKr = pl.SKr;
-    p.gps_r = pl.gps_r;
     p.n_r_units = g.r_mode == GLOWQ_R_COMPUTE ? pl.n_r_tiles * pl.SKr : 0;
     p.x_vec_ok = aligned16(x) && (g.x_stride % 8 == 0);
-    p.xs_stride = std::max(pl.gps, g.r_mode == GLOWQ_R_COMPUTE ? pl.gps_r : 0) * 256 + 64;
+    p.xs_stride = pl.xs_stride;
+    p.stages = pl.stages;
+    p.debug = g.reserved;
+    p.meta_gp = pl.meta_gp;
+    p.meta_gw = pl.meta_gw;
     int tb = 0;
     bool any_corr = false;
     for (int i = 0; i < g.n_members; ++i) {
@@ -218,8 +324,23 @@ int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cuda
 
     cudaError_t e;
     if (fast) {
-      if (gemv_smem_bytes(p, pl.NT) > 200 * 1024) return GLOWQ_ERR_UNSUPPORTED_SHAPE;
-      e = launch_gemv_fused(p, stream);
+      if (pl.stages < 2 || gemv_smem_bytes(p, pl.NT) > kSmemOnePerSm) return GLOWQ_ERR_UNSUPPORTED_SHAPE;
+      // persistent grid: every CTA resident at once, a whole number of CTAs per K slice
+      int grid = std::min(dev.sms * pl.ctas_per_sm, n_tiles * pl.SK);
+      grid = std::max(pl.SK, grid / pl.SK * pl.SK);
+      p.l_cols = std::min(std::max(p.rank, 8), 256);
+      alignas(64) TensorMaps tm;
+      std::memset(&tm, 0, sizeof(tm));
+      for (int i = 0; i < g.n_members; ++i) {
+        const MemberDev& d = p.mem[i];
+        int rc = tensor_map_2d(&tm.w[i], CU_TENSOR_MAP_DATA_TYPE_INT32, d.qweight, static_cast<uint64_t>(pl.G) * 16, d.OC,
+                               static_cast<uint64_t>(d.wstride) * 4, kChunkGroups * 16, kTileRows);
+        if (rc == GLOWQ_OK && d.L != nullptr && p.r_mode != GLOWQ_R_NONE)
+          rc = tensor_map_2d(&tm.l[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, d.L, p.rank, d.OC,
+                             static_cast<uint64_t>(d.Lstride) * 2, p.l_cols, kTileRows);
+        if (rc != GLOWQ_OK) return rc;
+      }
+      e = launch_gemv_stream(p, tm, pl.NT, grid, stream);
       if (e != cudaSuccess) return fail_cuda(e);
     } else {
       float* r32 = nullptr;

@@ -1,0 +1,755 @@
+// Weight-streaming corrected W4A16 kernel for small token counts (decode).  One launch computes, for every
+// member i of a group,   y_i = x . dequant(Q_i)^T + alpha_i * (x . R^T) . L_i^T + bias_i.
+//
+// Persistent CTAs (one or two per SM), each with ten warps:
+//   * warp 8 streams packed weights: for every 32-row tile of the CTA it issues one 2-D TMA copy per pipeline
+//     stage (32 rows x 8 quantisation groups = 16 KB) into a shared-memory ring guarded by mbarriers, and after
+//     a tile's weight stages the tile's rows of L_i.  It depends on no other warp's results, so HBM stays busy
+//     across tile boundaries, reductions and epilogues.
+//   * warp 9 fetches the tile's scales and zero-point words a few tiles ahead into a small metadata ring.
+//   * warps 0-7 consume: warp w owns group w of every stage.  Lane (g = lane/4, t = lane%4) reads rows g, g+8,
+//     g+16, g+24 with one 128-bit shared load each - the four lanes of a quad cover the 64 B of one group - masks
+//     the codes into fp16 subnormals (no conversion arithmetic) and feeds m16n8k16 tensor-core MMAs against the
+//     activations staged once per CTA in B-fragment order (tokens on the MMA N axis, so up to 8 tokens cost what
+//     one token costs).  Each group's fp32 result is scaled by its fp16 scale, and the zero-point is applied as
+//     -z * scale * sum(x over the group), in fp32.
+//   * r = R_g . x is produced inside the launch by "R units" (16 rows of R x 1024 columns) that consumer warps
+//     claim through a ticket before their first tile; the last unit of an R tile sums the partials in a fixed
+//     order, rounds r to fp16 into r_buf and bumps a release counter.  Because units are claimed by CTAs that
+//     are already running, the bounded wait before the first L_i epilogue never depends on an unscheduled CTA.
+//   * K can be sliced across CTAs; the last CTA to arrive at a tile sums the slices in slice order.
+// Every wait (mbarrier, release counter) is bounded; on expiry the kernel records a status word and drains.
+#include "common.cuh"
+#include "params.h"
+
+namespace glowq {
+
+namespace {
+
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr uint32_t kMbarSpinLimit = 1u << 14;  // x ~2 us suspended per failed try_wait
+constexpr uint32_t kSuspendHintNs = 2000;  // a waiting thread sleeps in hardware instead of burning issue slots
+
+// ---------------------------------------------------------------- mbarrier / bulk-copy primitives
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* b, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* b, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(b)), "r"(parity), "r"(kSuspendHintNs)
+      : "memory");
+  return ok != 0;
+}
+// 2-D tiled TMA copy: the box of `tmap` at element coordinates (x, y) -> dense rows at dst (128-byte aligned).
+// x * element size must be a multiple of 16 bytes.  No multicast: the box lands in this CTA only.
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tmap, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(dst)),
+      "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+// 4-byte asynchronous copy global -> shared (LDGSTS) and its completion hook on an mbarrier: the arrive fires
+// once all of this thread's earlier cp.async copies have landed; it counts as one of the barrier's arrivals.
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_mbar_arrive(uint64_t* b) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
+
+struct Ctx {
+  volatile int* abort_flag;
+  uint32_t* status;
+};
+
+// Bounded wait on one phase of an mbarrier.  false = gave up (status recorded, everybody drains).
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, const Ctx& cx) {
+  uint32_t spins = 0;
+  while (!mbar_try_wait(b, parity)) {
+    if ((++spins & 15u) == 0 && *cx.abort_flag) return false;
+    if (spins > kMbarSpinLimit) {
+      *cx.abort_flag = 1;
+      atomicExch(cx.status, 2u);
+      return false;
+    }
+  }
+  return true;
+}
+// ---------------------------------------------------------------- activations
+// Stage x[0:M, g0*128 : (g0+ng)*128) into shared memory in MMA B-fragment order: for token m and group gl,
+// 16-byte chunk (i*4 + t) holds the columns 32t+8i+{0,4,1,5,2,6,3,7} of that group, the ones at odd positions of
+// a packed word (1,5,3,7) multiplied by 1/16 (see the consumer loop), and xsum[gl][m] = sum of the group's x in
+// fp32 (for the zero-point term).  Consumer threads only.
+__device__ __forceinline__ void stage_x(const GemvParams& p, int g0, int ng, unsigned char* xs, float* xsum, int mpad) {
+  const int per_tok = ng * 16;
+  const int total = p.M * per_tok;
+  for (int base = 0; base < total; base += kConsumerThreads) {
+    const int idx = base + threadIdx.x;
+    const bool valid = idx < total;
+    const int m = valid ? idx / per_tok : 0;
+    const int c = valid ? idx - m * per_tok : 0;
+    const int gl = c >> 4, s = c & 15;  // s = 8-column block of the group, in source order
+    const int k = (g0 + gl) * kGroup + 8 * s;
+    const __half* src = p.x + static_cast<size_t>(m) * p.x_stride + k;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (valid) {
+      if (p.x_vec_ok && k + 8 <= p.IC) {
+        v = *reinterpret_cast<const uint4*>(src);
+      } else {
+        __align__(16) __half tmp[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) tmp[e] = (k + e < p.IC) ? src[e] : __float2half(0.f);
+        v = *reinterpret_cast<const uint4*>(tmp);
+      }
+    }
+    const __half2* h2 = reinterpret_cast<const __half2*>(&v);
+    float part = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __half22float2(h2[e]);
+      part += f.x + f.y;
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);  // the 16 lanes of one (m, gl)
+    if (valid) {
+      uint4 o4 = interleave_pairs(v);
+      o4.y = hmul2(o4.y, 0x2C002C00u);
+      o4.w = hmul2(o4.w, 0x2C002C00u);
+      const int i = s & 3, t = s >> 2;
+      *reinterpret_cast<uint4*>(xs + static_cast<size_t>(m) * p.xs_stride + (gl * 16 + i * 4 + t) * 16) = o4;
+      if (s == 0) xsum[gl * mpad + m] = part;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- shared-space (32-bit address) accessors
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float lds_h2f(uint32_t a) {
+  unsigned short v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+  return __half2float(__ushort_as_half(v));
+}
+__device__ __forceinline__ float2 lds_f2(uint32_t a) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void mbar_arrive_u32(uint32_t a) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(a) : "memory");
+}
+// Whole-warp bounded wait on one phase of an mbarrier (32-bit shared address).
+__device__ __forceinline__ bool mbar_wait_u32(uint32_t a, uint32_t parity, const Ctx& cx) {
+  uint32_t spins = 0;
+  for (;;) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(a), "r"(parity), "r"(kSuspendHintNs)
+        : "memory");
+    if (ok) return true;
+    if ((++spins & 15u) == 0 && *cx.abort_flag) return false;
+    if (spins > kMbarSpinLimit) {
+      *cx.abort_flag = 1;
+      atomicExch(cx.status, 2u);
+      return false;
+    }
+  }
+}
+
+// Sum the per-warp accumulators of NB fragment blocks; fin[b*128 + tok*16 + row] (tok < 8, row < 16) receives the
+// CTA's sum of block b.
+template <int NB>
+__device__ __forceinline__ void cross_warp_reduce(float (&acc)[NB][4], float* red, float* fin) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int b = 0; b < NB; ++b)
+    reinterpret_cast<float4*>(red)[(warp * NB + b) * 32 + lane] = make_float4(acc[b][0], acc[b][1], acc[b][2], acc[b][3]);
+  consumer_sync();
+  for (int e = threadIdx.x; e < NB * 128; e += kConsumerThreads) {
+    const int b = e >> 7, ln = (e & 127) >> 2, c = e & 3;
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) s += red[((w * NB + b) * 32 + ln) * 4 + c];
+    const int row = (ln >> 2) + ((c & 2) ? 8 : 0);
+    const int tok = (ln & 3) * 2 + (c & 1);
+    fin[b * 128 + tok * 16 + row] = s;
+  }
+  consumer_sync();
+}
+
+// Combine K-slice partial tiles: every slice stores its tile; the last arrival sums all slices in slice
+// order (deterministic) and returns true with the sum in fin.
+template <int NB>
+__device__ __forceinline__ bool splitk_combine(float* fin, float* partial_base, uint32_t* ctr, int slices, int ks,
+                                               volatile int* s_flag) {
+  constexpr int kElems = NB * 128;
+  float* mine = partial_base + static_cast<size_t>(ks) * kElems;
+  for (int e = threadIdx.x; e < kElems; e += kConsumerThreads) mine[e] = fin[e];
+  __threadfence();
+  consumer_sync();
+  if (threadIdx.x == 0) {
+    const uint32_t old = atomicAdd(ctr, 1u);
+    *s_flag = (old == static_cast<uint32_t>(slices - 1));
+  }
+  consumer_sync();
+  const bool last = (*s_flag != 0);
+  if (last) {
+    __threadfence();
+    for (int e = threadIdx.x; e < kElems; e += kConsumerThreads) {
+      float s = 0.f;
+      for (int k = 0; k < slices; ++k) s += ldg_cg_f32(partial_base + static_cast<size_t>(k) * kElems + e);
+      fin[e] = s;
+    }
+    if (threadIdx.x == 0) *ctr = 0u;  // ready for the next launch that uses this workspace
+  }
+  consumer_sync();
+  return last;
+}
+
+// One R unit: rows [16 rt, 16 rt + 16) of R times the columns of K slice ks (8 groups), tokens 0..M-1.
+template <int NT>
+__device__ __forceinline__ void r_unit(const GemvParams& p, int unit, float* red, float* fin, volatile int* s_flag) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int rt = unit / p.SKr, ks = unit - rt * p.SKr;
+  const int j0 = rt * kRTileRows;
+  const int gbase = ks * kChunkGroups, ng = min(kChunkGroups, p.G - gbase);
+  const __half* rowA = p.R + static_cast<size_t>(min(j0 + g, p.rank - 1)) * p.R_stride;
+  const __half* rowB = p.R + static_cast<size_t>(min(j0 + g + 8, p.rank - 1)) * p.R_stride;
+  float acc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+  if (warp < ng) {
+    const int kb = (gbase + warp) * kGroup + 32 * t;
+    uint4 a[4], b[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = kb + 8 * i;
+      const bool ok = (k + 8 <= p.IC);
+      a[i] = ok ? ldg_stream_v4(rowA + k) : make_uint4(0, 0, 0, 0);
+      b[i] = ok ? ldg_stream_v4(rowB + k) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int tok = nt * 8 + g;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int k = kb + 8 * i;
+        uint4 xv = make_uint4(0, 0, 0, 0);
+        if (tok < p.M && k + 8 <= p.IC) {
+          const __half* src = p.x + static_cast<size_t>(tok) * p.x_stride + k;
+          if (p.x_vec_ok) {
+            xv = *reinterpret_cast<const uint4*>(src);
+          } else {
+            __align__(16) __half tmp[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) tmp[e] = src[e];
+            xv = *reinterpret_cast<const uint4*>(tmp);
+          }
+        }
+        mma16816(acc[nt], a[i].x, b[i].x, a[i].y, b[i].y, xv.x, xv.y);
+        mma16816(acc[nt], a[i].z, b[i].z, a[i].w, b[i].w, xv.z, xv.w);
+      }
+    }
+  }
+  cross_warp_reduce<NT>(acc, red, fin);
+  bool finalize = true;
+  if (p.SKr > 1)
+    finalize = splitk_combine<NT>(fin, p.r_partial + static_cast<size_t>(rt) * p.SKr * (NT * 128), p.r_tile_ctr + rt,
+                                  p.SKr, ks, s_flag);
+  if (finalize) {
+    for (int e = threadIdx.x; e < p.M * 16; e += kConsumerThreads) {
+      const int tok = e >> 4, r = e & 15;
+      if (j0 + r < p.rank)
+        p.r_buf[static_cast<size_t>(tok) * p.rank + j0 + r] = __float2half_rn(fin[(tok >> 3) * 128 + (tok & 7) * 16 + r]);
+    }
+    __threadfence();
+    consumer_sync();
+    if (threadIdx.x == 0) atomicAdd(p.ws_head + WS_R_DONE, 1u);
+  }
+}
+
+struct TileInfo {
+  int mi, row0;
+  bool corr;
+};
+__device__ __forceinline__ TileInfo tile_info(const GemvParams& p, int tile, int slice) {
+  int mi = 0;
+#pragma unroll
+  for (int i = 1; i < kMaxMembers; ++i)
+    if (i < p.n_members && tile >= p.mem[i].tile_begin) mi = i;
+  TileInfo ti;
+  ti.mi = mi;
+  ti.row0 = (tile - p.mem[mi].tile_begin) * kTileRows;
+  ti.corr = (slice == 0) && (p.r_mode != 0) && (p.mem[mi].L != nullptr) && (p.mem[mi].alpha != 0.f);
+  return ti;
+}
+
+template <int NT>
+__global__ void __launch_bounds__(kGemvThreads, (NT <= 2) ? 2 : 1)
+gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__ TensorMaps tm) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ int s_abort, s_flag, s_ticket;
+  constexpr int RT = kRowTiles;
+  constexpr int NB = RT * NT;  // 16-row x 8-token fragment blocks per tile
+
+  // shared-memory carve-up (must match gemv_smem_bytes)
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);
+  uint64_t* empty_bar = full_bar + kMaxStages;
+  uint64_t* meta_full = empty_bar + kMaxStages;
+  uint64_t* meta_empty = meta_full + kMetaDepth;
+  unsigned char* ring = smem + 256;
+  const int meta_bytes = kTileRows * (p.meta_gp * 2 + p.meta_gw * 4);
+  unsigned char* meta = ring + static_cast<size_t>(p.stages) * kStageBytes;
+  float* red = reinterpret_cast<float*>(meta + static_cast<size_t>(kMetaDepth) * meta_bytes);
+  float* fin = red + kConsumerWarps * NB * 128;
+  float* xsum = fin + NB * 128;                      // [groups of the slice][8 NT]
+  unsigned char* xs = reinterpret_cast<unsigned char*>(xsum + p.gps * (8 * NT));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int S = p.stages;
+  const int slice = blockIdx.x % p.SK;
+  const int first_tile = blockIdx.x / p.SK;
+  const int tile_step = gridDim.x / p.SK;
+  const int g0 = slice * p.gps;
+  const int ng = min(p.G, g0 + p.gps) - g0;
+  const int n_chunks = (ng + kChunkGroups - 1) / kChunkGroups;
+  const int n_lstages = (p.rank + 255) >> 8;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int i = 0; i < kMaxStages; ++i) {
+      mbar_init(full_bar + i, 1);
+      mbar_init(empty_bar + i, kConsumerWarps);
+    }
+    for (int i = 0; i < kMetaDepth; ++i) {
+      mbar_init(meta_full + i, 32);
+      mbar_init(meta_empty + i, kConsumerWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  Ctx cx{&s_abort, p.ws_head + WS_STATUS};
+  const uint32_t full_u32 = smem_u32(full_bar), empty_u32 = smem_u32(empty_bar);
+  const uint32_t mfull_u32 = smem_u32(meta_full), mempty_u32 = smem_u32(meta_empty);
+
+  if (warp == kConsumerWarps) {
+    // ================================================================ weight / L copy warp
+    // One 2-D TMA copy per pipeline stage: kTileRows rows x 512 B of packed weights (or x l_cols of L).  Per-row
+    // bulk copies of 512 B cap the copy engine at a fraction of HBM rate; one 16 KB box per instruction does not.
+    uint32_t st = 0, ph = 0, issued = 0;
+    bool ok = true;
+    for (int tile = first_tile; tile < p.n_tiles && ok; tile += tile_step) {
+      const TileInfo ti = tile_info(p, tile, slice);
+      for (int c = 0; c < n_chunks; ++c) {
+        if (!(ok = mbar_wait_u32(empty_u32 + st * 8, ph ^ 1, cx))) break;
+        if (lane == 0) {
+          if (p.debug & 2) {
+            mbar_arrive(full_bar + st);
+          } else {
+            mbar_arrive_expect_tx(full_bar + st, kStageBytes);
+            tma_load_2d(ring + static_cast<size_t>(st) * kStageBytes, &tm.w[ti.mi], (g0 + c * kChunkGroups) * 16, ti.row0,
+                        full_bar + st);
+          }
+        }
+        ++issued;
+        if (++st == static_cast<uint32_t>(S)) {
+          st = 0;
+          ph ^= 1;
+        }
+      }
+      if (ok && ti.corr) {
+        for (int l = 0; l < n_lstages; ++l) {
+          if (!(ok = mbar_wait_u32(empty_u32 + st * 8, ph ^ 1, cx))) break;
+          if (lane == 0) {
+            mbar_arrive_expect_tx(full_bar + st, static_cast<uint32_t>(p.l_cols) * 2u * kTileRows);
+            tma_load_2d(ring + static_cast<size_t>(st) * kStageBytes, &tm.l[ti.mi], 256 * l, ti.row0, full_bar + st);
+          }
+          ++issued;
+          if (++st == static_cast<uint32_t>(S)) {
+            st = 0;
+            ph ^= 1;
+          }
+        }
+      }
+    }
+    if (!ok && !(p.debug & 2)) {
+      // Draining: copies already issued still land in this CTA's shared memory; wait (bounded) for them so that
+      // the CTA does not retire under an in-flight copy.
+      for (uint32_t j = (issued > static_cast<uint32_t>(S) ? issued - S : 0); j < issued; ++j) {
+        uint32_t spins = 0;
+        while (!mbar_try_wait(full_bar + (j % S), (j / S) & 1) && ++spins < kMbarSpinLimit) {
+        }
+      }
+    }
+  } else if (warp == kConsumerWarps + 1) {
+    // ================================================================ metadata warp: lane r fetches row r
+    uint32_t slot = 0, ph = 0;
+    bool ok = true;
+    for (int tile = first_tile; tile < p.n_tiles && ok; tile += tile_step) {
+      const TileInfo ti = tile_info(p, tile, slice);
+      const MemberDev& mb = p.mem[ti.mi];
+      if (!(ok = mbar_wait_u32(mempty_u32 + slot * 8, ph ^ 1, cx))) break;
+      const int row = min(ti.row0 + lane, mb.OC - 1);
+      unsigned char* mbase = meta + static_cast<size_t>(slot) * meta_bytes;
+      __half* ms = reinterpret_cast<__half*>(mbase) + lane * p.meta_gp;
+      uint32_t* mz = reinterpret_cast<uint32_t*>(mbase + kTileRows * p.meta_gp * 2) + lane * p.meta_gw;
+      const __half* srow = mb.scales + static_cast<size_t>(row) * mb.sstride + g0;
+      // Asynchronous 4-byte copies: the warp never waits for its own loads, so several tiles of metadata are in
+      // flight at once (a synchronous load/store loop here costs a DRAM round trip per tile and throttles the CTA).
+      if (((mb.sstride | g0) & 1) == 0 && ((reinterpret_cast<uintptr_t>(mb.scales) & 3) == 0)) {
+        const int np_full = ng >> 1;
+        for (int pi = 0; pi < np_full; ++pi) cp_async4(ms + 2 * pi, srow + 2 * pi);
+        if (ng & 1) ms[ng - 1] = srow[ng - 1];  // odd tail: there may be no 4 readable bytes at the end of a row
+      } else {
+        for (int gl = 0; gl < ng; ++gl) ms[gl] = srow[gl];
+      }
+      const int32_t* zrow = mb.qzeros + static_cast<size_t>(row) * mb.zstride + (g0 >> 3);
+      const int nw = (ng + 7) >> 3;
+      for (int wi = 0; wi < nw; ++wi) cp_async4(mz + wi, zrow + wi);
+      cp_async_mbar_arrive(meta_full + slot);
+      if (++slot == kMetaDepth) {
+        slot = 0;
+        ph ^= 1;
+      }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");  // nothing of this warp is in flight when the CTA retires
+  } else {
+    // ================================================================ consumer warps
+    const int g = lane >> 2, t = lane & 3;
+    stage_x(p, g0, ng, xs, xsum, 8 * NT);
+    if (p.r_mode == 1) {
+      for (;;) {
+        consumer_sync();  // also orders s_ticket reuse and, first time round, publishes xs
+        if (threadIdx.x == 0) s_ticket = static_cast<int>(atomicAdd(p.ws_head + WS_TICKET, 1u));
+        consumer_sync();
+        const int u = s_ticket;
+        if (u >= p.n_r_units) break;
+        r_unit<NT>(p, u, red, fin, &s_flag);
+      }
+    }
+    consumer_sync();
+
+    // per-lane constant shared addresses: weight quad (warp's group, lane's 16 B, lane's row), x chunk, x sums
+    const uint32_t ring_lane = smem_u32(ring) + warp * 64 + t * 16 + g * kRowPitch;
+    const uint32_t x_lane = smem_u32(xs) + g * p.xs_stride + t * 16;
+    const uint32_t xsum_lane = smem_u32(xsum) + t * 8;
+    const uint32_t xtok8 = 8u * p.xs_stride;
+    const uint32_t meta_u32 = smem_u32(meta);
+    const uint32_t zshift = warp * 4;  // group gl = 8 c + warp: zero nibble `warp` of zero word c
+    bool tokv[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) tokv[nt] = (nt * 8 + g) < p.M;
+
+    uint32_t st = 0, ph = 0, slot = 0, mph = 0;
+    bool ok = true, r_ready = (p.r_mode != 1);
+    for (int tile = first_tile; tile < p.n_tiles; tile += tile_step) {
+      const TileInfo ti = tile_info(p, tile, slice);
+      const MemberDev& mb = p.mem[ti.mi];
+      ok = ok && mbar_wait_u32(mfull_u32 + slot * 8, mph, cx);
+      const uint32_t ms_lane = meta_u32 + slot * meta_bytes + (g * p.meta_gp + warp) * 2;
+      const uint32_t mz_lane = meta_u32 + slot * meta_bytes + kTileRows * p.meta_gp * 2 + g * p.meta_gw * 4;
+      const uint32_t ms_row8 = 8u * p.meta_gp * 2, mz_row8 = 8u * p.meta_gw * 4;
+
+      float acc[NB][4];
+#pragma unroll
+      for (int b = 0; b < NB; ++b) acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.f;
+
+      // Codes go to the tensor cores as fp16 SUBNORMALS: (w & 0x000F000F) is half2(n0, n4) * 2^-24 and
+      // (w & 0x00F000F0) is half2(n1, n5) * 2^-20, exactly, with no conversion arithmetic at all; the matching
+      // activations were staged divided by 16, so every product carries the factor 2^-24, which goes into the
+      // group's scale.  The zero-point leaves the inner loop too:
+      //   sum_k (n_k - z) x_k = sum_k n_k x_k - z * sum_k x_k,   with sum_k x_k staged per (group, token).
+      for (int c = 0; c < n_chunks; ++c) {
+        ok = ok && mbar_wait_u32(full_u32 + st * 8, ph, cx);
+        const int gl = c * kChunkGroups + warp;
+        if (ok && gl < ng && !(p.debug & 1)) {
+          const uint32_t wbase = ring_lane + st * kStageBytes;
+          uint4 W[RT][2];
+#pragma unroll
+          for (int j = 0; j < RT; ++j) {
+            W[j][0] = lds128(wbase + (j * 16) * kRowPitch);
+            W[j][1] = lds128(wbase + (j * 16 + 8) * kRowPitch);
+          }
+          float ag[RT][NT][4];
+#pragma unroll
+          for (int j = 0; j < RT; ++j)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) ag[j][nt][0] = ag[j][nt][1] = ag[j][nt][2] = ag[j][nt][3] = 0.f;
+          const uint32_t xg = x_lane + gl * 256;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            constexpr uint32_t MLO = 0x000F000Fu, MHI = 0x00F000F0u;
+            uint4 xb[NT];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) xb[nt] = tokv[nt] ? lds128(xg + nt * xtok8 + i * 64) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int j = 0; j < RT; ++j) {
+              const uint32_t a = (i == 0) ? W[j][0].x : (i == 1) ? W[j][0].y : (i == 2) ? W[j][0].z : W[j][0].w;
+              const uint32_t b = (i == 0) ? W[j][1].x : (i == 1) ? W[j][1].y : (i == 2) ? W[j][1].z : W[j][1].w;
+              const uint32_t a8 = a >> 8, b8 = b >> 8;
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt) {
+                mma16816(ag[j][nt], a & MLO, b & MLO, a & MHI, b & MHI, xb[nt].x, xb[nt].y);
+                mma16816(ag[j][nt], a8 & MLO, b8 & MLO, a8 & MHI, b8 & MHI, xb[nt].z, xb[nt].w);
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < RT; ++j) {
+            const float sA = lds_h2f(ms_lane + j * 2 * ms_row8 + c * 16);
+            const float sB = lds_h2f(ms_lane + j * 2 * ms_row8 + ms_row8 + c * 16);
+            const float zA = static_cast<float>((lds32(mz_lane + j * 2 * mz_row8 + c * 4) >> zshift) & 0xFu);
+            const float zB = static_cast<float>((lds32(mz_lane + j * 2 * mz_row8 + mz_row8 + c * 4) >> zshift) & 0xFu);
+            const float sA24 = sA * 16777216.f, sB24 = sB * 16777216.f, szA = -sA * zA, szB = -sB * zB;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+              const float2 xs2 = lds_f2(xsum_lane + gl * (32 * NT) + nt * 32);
+              float* a4 = acc[j * NT + nt];
+              a4[0] = fmaf(sA24, ag[j][nt][0], fmaf(szA, xs2.x, a4[0]));
+              a4[1] = fmaf(sA24, ag[j][nt][1], fmaf(szA, xs2.y, a4[1]));
+              a4[2] = fmaf(sB24, ag[j][nt][2], fmaf(szB, xs2.x, a4[2]));
+              a4[3] = fmaf(sB24, ag[j][nt][3], fmaf(szB, xs2.y, a4[3]));
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive_u32(empty_u32 + st * 8);
+        if (++st == static_cast<uint32_t>(S)) {
+          st = 0;
+          ph ^= 1;
+        }
+      }
+
+      if (ti.corr) {
+        if (!r_ready) {  // r comes from R units of this launch: bounded wait on the release counter
+          if (lane == 0) {
+            uint32_t spins = 0;
+            while (ld_acquire_u32(p.ws_head + WS_R_DONE) < static_cast<uint32_t>(p.n_r_tiles)) {
+              __nanosleep(100);
+              if (s_abort || ++spins > kSpinLimit) {
+                s_abort = 1;
+                atomicExch(p.ws_head + WS_STATUS, 1u);
+                break;
+              }
+            }
+          }
+          __syncwarp();
+          r_ready = true;
+        }
+        float al[NB][4];
+#pragma unroll
+        for (int b = 0; b < NB; ++b) al[b][0] = al[b][1] = al[b][2] = al[b][3] = 0.f;
+        for (int l = 0; l < n_lstages; ++l) {
+          ok = ok && mbar_wait_u32(full_u32 + st * 8, ph, cx);
+          const int cols = min(256, p.rank - 256 * l);
+          const int k = 32 * warp + 8 * t;  // column inside this L stage
+          if (ok && 32 * warp < cols) {  // warp-uniform: every lane of the warp takes part in the MMAs below
+            const bool kin = k < cols;     // lanes past the last column of a narrow factor feed zeros
+            const uint32_t lpitch = static_cast<uint32_t>(p.l_cols) * 2u;  // dense rows of the L box
+            const uint32_t lbase = smem_u32(ring) + st * kStageBytes + g * lpitch + k * 2;
+            uint4 rb[NT];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+              rb[nt] = (kin && tokv[nt]) ? ldg_cg_v4(p.r_buf + static_cast<size_t>(nt * 8 + g) * p.rank + 256 * l + k)
+                                         : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int j = 0; j < RT; ++j) {
+              const uint4 la = kin ? lds128(lbase + (j * 16) * lpitch) : make_uint4(0, 0, 0, 0);
+              const uint4 lb = kin ? lds128(lbase + (j * 16 + 8) * lpitch) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt) {
+                mma16816(al[j * NT + nt], la.x, lb.x, la.y, lb.y, rb[nt].x, rb[nt].y);
+                mma16816(al[j * NT + nt], la.z, lb.z, la.w, lb.w, rb[nt].z, rb[nt].w);
+              }
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive_u32(empty_u32 + st * 8);
+          if (++st == static_cast<uint32_t>(S)) {
+            st = 0;
+            ph ^= 1;
+          }
+        }
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) acc[b][c] = fmaf(mb.alpha, al[b][c], acc[b][c]);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive_u32(mempty_u32 + slot * 8);
+      if (++slot == kMetaDepth) {
+        slot = 0;
+        mph ^= 1;
+      }
+
+      cross_warp_reduce<NB>(acc, red, fin);
+      bool finalize = true;
+      if (p.SK > 1)
+        finalize = splitk_combine<NB>(fin, p.sk_partial + static_cast<size_t>(tile) * p.SK * (NB * 128), p.tile_ctr + tile,
+                                      p.SK, slice, &s_flag);
+      if (finalize) {
+        // fin[(j*NT + nt)*128 + tok8*16 + r]: row = row0 + 16 j + r, token = 8 nt + tok8
+        for (int e = threadIdx.x; e < p.M * kTileRows; e += kConsumerThreads) {
+          const int tok = e / kTileRows, rr = e - tok * kTileRows, row = ti.row0 + rr;
+          if (row < mb.OC) {
+            float v = fin[((rr >> 4) * NT + (tok >> 3)) * 128 + (tok & 7) * 16 + (rr & 15)];
+            if (mb.bias) v += __half2float(mb.bias[row]);
+            const size_t o = static_cast<size_t>(tok) * mb.out_stride + row;
+            if (p.out_fp32)
+              static_cast<float*>(mb.out)[o] = v;
+            else
+              static_cast<__half*>(mb.out)[o] = __float2half_rn(v);
+          }
+        }
+      }
+    }
+  }
+
+  __syncthreads();
+  if (p.r_mode == 1 && threadIdx.x == 0) {
+    const uint32_t old = atomicAdd(p.ws_head + WS_EXIT, 1u);
+    if (old == gridDim.x - 1) {  // last CTA out re-arms the counters for the next launch
+      p.ws_head[WS_TICKET] = 0u;
+      p.ws_head[WS_R_DONE] = 0u;
+      p.ws_head[WS_EXIT] = 0u;
+      __threadfence();
+    }
+  }
+}
+
+// Any-shape scalar kernel for layouts the streaming kernel does not take (group_size != 128, packed
+// rows that are not 16-byte aligned).  One warp per output row; fp32 accumulation.
+__global__ void __launch_bounds__(256) w4a16_generic_kernel(const __half* x, const int32_t* qweight, const __half* scales,
+                                                           const int32_t* qzeros, const __half* bias, const __half* L,
+                                                           const float* r32, float alpha, void* out, int out_fp32,
+                                                           int M, int IC, int OC, int rank, int group_size, int x_stride,
+                                                           int wstride, int zstride, int sstride, int Lstride,
+                                                           int out_stride) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= OC) return;
+  const int32_t* wrow = qweight + static_cast<size_t>(row) * wstride;
+  const int32_t* zrow = qzeros + static_cast<size_t>(row) * zstride;
+  for (int m = 0; m < M; ++m) {
+    float acc = 0.f;
+    for (int k = lane; k < IC; k += 32) {
+      const int G = k / group_size;
+      const float w = static_cast<float>(static_cast<int>(nibble(wrow, k)) - static_cast<int>(nibble(zrow, G))) *
+                      __half2float(scales[static_cast<size_t>(row) * sstride + G]);
+      acc = fmaf(w, __half2float(x[static_cast<size_t>(m) * x_stride + k]), acc);
+    }
+    float c = 0.f;
+    if (L != nullptr && r32 != nullptr)
+      for (int j = lane; j < rank; j += 32)
+        c = fmaf(__half2float(L[static_cast<size_t>(row) * Lstride + j]), r32[static_cast<size_t>(m) * rank + j], c);
+    acc = fmaf(alpha, c, acc);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+      if (bias) acc += __half2float(bias[row]);
+      const size_t oidx = static_cast<size_t>(m) * out_stride + row;
+      if (out_fp32)
+        static_cast<float*>(out)[oidx] = acc;
+      else
+        static_cast<__half*>(out)[oidx] = __float2half_rn(acc);
+    }
+  }
+}
+
+// r32[M, rank] = x . R^T for the generic path (one warp per (token, rank row)); also rounds to r_buf.
+__global__ void __launch_bounds__(256) r_generic_kernel(const __half* x, const __half* R, float* r32, __half* r_buf, int M,
+                                                       int IC, int rank, int x_stride, int R_stride) {
+  const int w = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (w >= M * rank) return;
+  const int m = w / rank, j = w - m * rank;
+  float acc = 0.f;
+  for (int k = lane; k < IC; k += 32)
+    acc = fmaf(__half2float(R[static_cast<size_t>(j) * R_stride + k]), __half2float(x[static_cast<size_t>(m) * x_stride + k]), acc);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) {
+    const __half h = __float2half_rn(acc);
+    r_buf[static_cast<size_t>(m) * rank + j] = h;
+    r32[static_cast<size_t>(m) * rank + j] = __half2float(h);
+  }
+}
+
+__global__ void __launch_bounds__(256) r_widen_kernel(const __half* r_buf, float* r32, int n) {
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i < n) r32[i] = __half2float(r_buf[i]);
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------- host launchers (called from abi.cu)
+size_t gemv_smem_bytes(const GemvParams& p, int NT) {
+  size_t off = 256;
+  off += static_cast<size_t>(p.stages) * kStageBytes;
+  off += static_cast<size_t>(kMetaDepth) * kTileRows * (p.meta_gp * 2 + p.meta_gw * 4);
+  off += static_cast<size_t>(kConsumerWarps + 1) * kRowTiles * NT * 512;
+  off += static_cast<size_t>(p.gps) * NT * 32;
+  off += static_cast<size_t>(p.M) * p.xs_stride;
+  return off;
+}
+
+template <int NT>
+static cudaError_t launch_nt(const GemvParams& p, const TensorMaps& tm, int grid, cudaStream_t stream) {
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    if (e != cudaSuccess) return e;
+    attr_done[dev] = true;
+  }
+  gemv_stream_kernel<NT><<<grid, kGemvThreads, gemv_smem_bytes(p, NT), stream>>>(p, tm);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gemv_stream(const GemvParams& p, const TensorMaps& tm, int NT, int grid, cudaStream_t stream) {
+  if (NT <= 1) return launch_nt<1>(p, tm, grid, stream);
+  if (NT <= 2) return launch_nt<2>(p, tm, grid, stream);
+  return launch_nt<4>(p, tm, grid, stream);
+}
+
+cudaError_t launch_generic_r(const __half* x, const __half* R, __half* r_buf, float* r32, int r_mode, int M, int IC,
+                             int rank, int x_stride, int R_stride, cudaStream_t stream) {
+  if (r_mode == 1)
+    r_generic_kernel<<<(M * rank + 7) / 8, 256, 0, stream>>>(x, R, r32, r_buf, M, IC, rank, x_stride, R_stride);
+  else
+    r_widen_kernel<<<(M * rank + 255) / 256, 256, 0, stream>>>(r_buf, r32, M * rank);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_generic(const __half* x, const MemberDev& mb, const float* r32, int out_fp32, int M, int IC, int rank,
+                           int group_size, int x_stride, cudaStream_t stream) {
+  const bool corr = r32 != nullptr && mb.L != nullptr && mb.alpha != 0.f;
+  w4a16_generic_kernel<<<(mb.OC + 7) / 8, 256, 0, stream>>>(x, mb.qweight, mb.scales, mb.qzeros, mb.bias,
+                                                           corr ? mb.L : nullptr, corr ? r32 : nullptr, mb.alpha, mb.out,
+                                                           out_fp32, M, IC, mb.OC, rank, group_size, x_stride, mb.wstride,
+                                                           mb.zstride, mb.sstride, mb.Lstride, mb.out_stride);
+  return cudaGetLastError();
+}
+
+}  // namespace glowq

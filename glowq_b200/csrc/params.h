@@ -1,5 +1,6 @@
 // Launch descriptors passed by value to the kernels, and the workspace layout.
 #pragma once
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -7,16 +8,23 @@
 namespace glowq {
 
 constexpr int kMaxMembers = 4;
-constexpr int kTileRows = 16;      // output rows per CTA of the weight-streaming kernel (one MMA M tile)
-constexpr int kGemvWarps = 8;
-constexpr int kGemvThreads = kGemvWarps * 32;
-constexpr int kGroup = 128;        // quantisation group of the fast paths
-constexpr unsigned kSpinLimit = 1u << 21;  // bounded device-side waits (x >= 200 ns each)
+constexpr int kRowTiles = 2;        // MMA M tiles (16 rows) per work item of the weight-streaming kernel
+constexpr int kTileRows = 16 * kRowTiles;  // output rows per work item
+constexpr int kRTileRows = 16;      // rows of R per R unit
+constexpr int kConsumerWarps = 8;   // warps that dequantise + MMA; warp w takes group w of every chunk
+constexpr int kGemvThreads = (kConsumerWarps + 2) * 32;  // + weight-copy warp + metadata warp
+constexpr int kGroup = 128;         // quantisation group of the fast paths
+constexpr int kChunkGroups = 8;     // groups per pipeline stage: 1024 input columns = 512 packed bytes per row
+constexpr int kRowPitch = kChunkGroups * 64;  // stage row pitch in shared memory: the dense box a 2-D TMA copy writes
+constexpr int kStageBytes = kTileRows * kRowPitch;
+constexpr int kMetaDepth = 3;       // tiles of scale / zero-point metadata in flight
+constexpr int kMaxStages = 8;
+constexpr unsigned kSpinLimit = 1u << 18;  // bound of every device-side wait loop
 
 // Workspace header (uint32 words); the rest of the workspace follows at kWsHeaderBytes.
 enum : int { WS_TICKET = 0, WS_R_DONE = 1, WS_EXIT = 2, WS_STATUS = 3, WS_HEADER_WORDS = 64 };
 constexpr size_t kWsHeaderBytes = WS_HEADER_WORDS * 4;
-constexpr int kMaxRTiles = 64;     // rank <= 1024
+constexpr int kMaxRTiles = 64;      // rank <= 1024
 
 struct MemberDev {
   const int32_t* qweight;
@@ -27,7 +35,14 @@ struct MemberDev {
   void* out;
   int OC, wstride, zstride, sstride, Lstride, out_stride;
   float alpha;
-  int tile_begin;   // index of this member's first 16-row tile in the group's tile list
+  int tile_begin;   // index of this member's first row tile (kTileRows rows) in the group's tile list
+};
+
+// TMA descriptors of every member's packed weight ([OC, G*16] int32, box 128 x kTileRows) and left factor
+// ([OC, rank] fp16, box l_cols x kTileRows).  Rows or columns of a box that fall outside the tensor read as zero.
+struct alignas(64) TensorMaps {
+  CUtensorMap w[kMaxMembers];
+  CUtensorMap l[kMaxMembers];
 };
 
 struct GemvParams {
@@ -36,15 +51,19 @@ struct GemvParams {
   __half* r_buf;
   uint32_t* ws_head;      // header words
   uint32_t* r_tile_ctr;   // [n_r_tiles] arrival counters of the r partial sums
-  float* r_partial;       // [n_r_tiles][SKr][16][Mpad]
+  float* r_partial;       // [n_r_tiles][SKr][NT*128]
   uint32_t* tile_ctr;     // [n_tiles] arrival counters of the split-K partial sums
-  float* sk_partial;      // [n_tiles][SK][16][Mpad]
+  float* sk_partial;      // [n_tiles][SK][kRowTiles*NT*128]
   int M, IC, x_stride, R_stride, G, rank, r_mode, out_fp32, n_members;
-  int n_tiles, SK, gps;          // main work: tiles x K slices, groups per slice
-  int n_r_tiles, SKr, gps_r;     // r work
+  int n_tiles, SK, gps;          // main work: tiles x K slices, groups per slice (multiple of kChunkGroups)
+  int n_r_tiles, SKr;            // r work: 16-row tiles of R x K slices of kChunkGroups groups
   int n_r_units;                 // n_r_tiles * SKr (0 unless r_mode == COMPUTE)
   int x_vec_ok;                  // x rows are 16-byte aligned
   int xs_stride;                 // bytes between tokens of the staged x slice in shared memory
+  int stages;                    // weight ring depth
+  int debug;                     // tuning experiments only (0 in production)
+  int l_cols;                    // columns of L per pipeline stage: min(rank, 256)
+  int meta_gp, meta_gw;          // per-row metadata pitch: scale halves, zero words (of one K slice)
   MemberDev mem[kMaxMembers];
 };
 

@@ -157,6 +157,19 @@ def test_golden_forward_vectors(golden_forward, tag, d, rank, bias, M, alpha):
             assert_close(out, f[f"{tag}.y.M{M}.{od}.a{alpha}.{n}"].astype(np.float32), tag=f"{n} {od}")
 
 
+@pytest.mark.parametrize("rank", [8, 16, 24, 40, 72, 264])
+def test_ranks_that_are_not_multiples_of_32(rank):
+    rng = np.random.default_rng(rank)
+    lin = Linear(rng, 80, 1024, rank=rank, bias=True)
+    R = (rng.standard_normal((rank, 1024)) * 0.01).astype(np.float16)
+    x = rng.standard_normal((9, 1024)).astype(np.float16)
+    out = new_out(9, lin)
+    r_buf = torch.zeros(9, rank, dtype=torch.float16, device="cuda")
+    g = make_group(dev(x), [lin], [out], R_d=dev(R), r_buf=r_buf, r_mode=K.R_COMPUTE)
+    assert run_group(g) == 0 and status_ok(g) == 0
+    assert_close(out, lin.oracle(x, R))
+
+
 def test_mixed_group_members_alpha_and_missing_L():
     """gate/up style group where one member is uncorrected and alphas differ."""
     rng = np.random.default_rng(3)
