@@ -137,7 +137,7 @@ int env_int(const char* name, int dflt) {
 
 // Launch plan of the weight-streaming kernel (K slices, pipeline depth, grid) and the workspace carve-up.
 struct GemvPlan {
-  int NT, G, n_tiles, SK, gps, n_r_tiles, SKr, stages, ctas_per_sm, meta_gp, meta_gw, xs_stride;
+  int NT, G, n_tiles, SK, gps, n_r_tiles, SKr, gpr, stages, ctas_per_sm, meta_gp, meta_gw, xs_stride;
   size_t smem;
   size_t off_r_ctr, off_tile_ctr, off_r_partial, off_sk_partial, off_r32, total;
 };
@@ -145,7 +145,8 @@ struct GemvPlan {
 size_t plan_smem(const GemvPlan& pl, int Mc, int stages) {
   return 256 + static_cast<size_t>(stages) * kStageBytes +
          static_cast<size_t>(kMetaDepth) * kTileRows * (pl.meta_gp * 2 + pl.meta_gw * 4) +
-         static_cast<size_t>(kConsumerWarps + 1) * kRowTiles * pl.NT * 512 + static_cast<size_t>(pl.gps) * pl.NT * 32 +
+         static_cast<size_t>(2 * kConsumerWarps) * kRowTiles * pl.NT * 512 + static_cast<size_t>(pl.NT) * 512 +
+         static_cast<size_t>(pl.gps) * pl.NT * 32 +
          static_cast<size_t>(Mc) * pl.xs_stride;
 }
 
@@ -188,7 +189,7 @@ GemvPlan make_plan(int M, int IC, int n_tiles, int rank, int sms, int split_k) {
   if (forced_stages > 0 && pl.stages > 0) pl.stages = std::max(2, std::min(forced_stages, pl.stages));
   pl.smem = plan_smem(pl, Mc, pl.stages);
   pl.n_r_tiles = ceil_div(std::max(rank, 0), kRTileRows);
-  pl.SKr = chunks;
+  pl.SKr = std::min(4, chunks);   // consumers add the K slices of r themselves: keep them few
   const size_t tile_elems = static_cast<size_t>(kRowTiles) * pl.NT * 128;
   size_t off = kWsHeaderBytes;
   pl.off_r_ctr = off;
@@ -196,7 +197,9 @@ GemvPlan make_plan(int M, int IC, int n_tiles, int rank, int sms, int split_k) {
   pl.off_tile_ctr = off;
   off = align_up(off + static_cast<size_t>(n_tiles) * 4, 256);
   pl.off_r_partial = off;
-  off = align_up(off + (pl.SKr > 1 ? static_cast<size_t>(pl.n_r_tiles) * pl.SKr * tile_elems * 4 : 0), 256);
+  pl.gpr = ceil_div(pl.G, pl.SKr);
+  pl.SKr = ceil_div(pl.G, pl.gpr);
+  off = align_up(off + static_cast<size_t>(pl.n_r_tiles) * pl.SKr * pl.NT * 128 * 4, 256);
   pl.off_sk_partial = off;
   off = align_up(off + (pl.SK > 1 ? static_cast<size_t>(n_tiles) * pl.SK * tile_elems * 4 : 0), 256);
   pl.off_r32 = off;
@@ -273,7 +276,6 @@ int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cuda
     p.R = static_cast<const __half*>(g.R);
     p.r_buf = r_buf;
     p.ws_head = reinterpret_cast<uint32_t*>(ws);
-    p.r_tile_ctr = reinterpret_cast<uint32_t*>(ws + pl.off_r_ctr);
     p.tile_ctr = reinterpret_cast<uint32_t*>(ws + pl.off_tile_ctr);
     p.r_partial = reinterpret_cast<float*>(ws + pl.off_r_partial);
     p.sk_partial = reinterpret_cast<float*>(ws + pl.off_sk_partial);
@@ -291,6 +293,7 @@ int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cuda
     p.gps = pl.gps;
     p.n_r_tiles = pl.n_r_tiles;
     p.SKr = pl.SKr;
+    p.gpr = pl.gpr;
     p.n_r_units = g.r_mode == GLOWQ_R_COMPUTE ? pl.n_r_tiles * pl.SKr : 0;
     p.x_vec_ok = aligned16(x) && (g.x_stride % 8 == 0);
     p.xs_stride = pl.xs_stride;

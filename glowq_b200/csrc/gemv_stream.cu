@@ -13,10 +13,10 @@
 //     activations staged once per CTA in B-fragment order (tokens on the MMA N axis, so up to 8 tokens cost what
 //     one token costs).  Each group's fp32 result is scaled by its fp16 scale, and the zero-point is applied as
 //     -z * scale * sum(x over the group), in fp32.
-//   * r = R_g . x is produced inside the launch by "R units" (16 rows of R x 1024 columns) that consumer warps
-//     claim through a ticket before their first tile; the last unit of an R tile sums the partials in a fixed
-//     order, rounds r to fp16 into r_buf and bumps a release counter.  Because units are claimed by CTAs that
-//     are already running, the bounded wait before the first L_i epilogue never depends on an unscheduled CTA.
+//   * r = R_g . x is produced inside the launch by "R units" (16 rows of R x 1024 columns) that the consumer warps
+//     of the last CTAs run before their first tile; the last unit of an R tile sums the partials in a fixed
+//     order, rounds r to fp16 into r_buf and bumps a release counter.  The grid never exceeds what is resident
+//     at once, so the bounded wait before the first L_i epilogue never depends on an unscheduled CTA.
 //   * K can be sliced across CTAs; the last CTA to arrive at a tile sums the slices in slice order.
 // Every wait (mbarrier, release counter) is bounded; on expiry the kernel records a status word and drains.
 #include "common.cuh"
@@ -72,64 +72,63 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;"
 struct Ctx {
   volatile int* abort_flag;
   uint32_t* status;
+  int mode;
 };
 
-// Bounded wait on one phase of an mbarrier.  false = gave up (status recorded, everybody drains).
-__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, const Ctx& cx) {
-  uint32_t spins = 0;
-  while (!mbar_try_wait(b, parity)) {
-    if ((++spins & 15u) == 0 && *cx.abort_flag) return false;
-    if (spins > kMbarSpinLimit) {
-      *cx.abort_flag = 1;
-      atomicExch(cx.status, 2u);
-      return false;
-    }
-  }
-  return true;
-}
 // ---------------------------------------------------------------- activations
 // Stage x[0:M, g0*128 : (g0+ng)*128) into shared memory in MMA B-fragment order: for token m and group gl,
 // 16-byte chunk (i*4 + t) holds the columns 32t+8i+{0,4,1,5,2,6,3,7} of that group, the ones at odd positions of
 // a packed word (1,5,3,7) multiplied by 1/16 (see the consumer loop), and xsum[gl][m] = sum of the group's x in
 // fp32 (for the zero-point term).  Consumer threads only.
 __device__ __forceinline__ void stage_x(const GemvParams& p, int g0, int ng, unsigned char* xs, float* xsum, int mpad) {
+  constexpr int kBatch = 4;  // global loads in flight per thread before any of them is consumed
   const int per_tok = ng * 16;
   const int total = p.M * per_tok;
-  for (int base = 0; base < total; base += kConsumerThreads) {
-    const int idx = base + threadIdx.x;
-    const bool valid = idx < total;
-    const int m = valid ? idx / per_tok : 0;
-    const int c = valid ? idx - m * per_tok : 0;
-    const int gl = c >> 4, s = c & 15;  // s = 8-column block of the group, in source order
-    const int k = (g0 + gl) * kGroup + 8 * s;
-    const __half* src = p.x + static_cast<size_t>(m) * p.x_stride + k;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (valid) {
-      if (p.x_vec_ok && k + 8 <= p.IC) {
-        v = *reinterpret_cast<const uint4*>(src);
-      } else {
-        __align__(16) __half tmp[8];
+  for (int base = 0; base < total; base += kConsumerThreads * kBatch) {
+    uint4 v[kBatch];
+    int mm[kBatch], cc[kBatch];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) tmp[e] = (k + e < p.IC) ? src[e] : __float2half(0.f);
-        v = *reinterpret_cast<const uint4*>(tmp);
+    for (int b = 0; b < kBatch; ++b) {
+      const int idx = base + b * kConsumerThreads + threadIdx.x;
+      const bool valid = idx < total;
+      const int m = valid ? idx / per_tok : 0;
+      const int c = valid ? idx - m * per_tok : -1;
+      mm[b] = m;
+      cc[b] = c;
+      v[b] = make_uint4(0, 0, 0, 0);
+      if (valid) {
+        const int k = (g0 + (c >> 4)) * kGroup + 8 * (c & 15);
+        const __half* src = p.x + static_cast<size_t>(m) * p.x_stride + k;
+        if (p.x_vec_ok && k + 8 <= p.IC) {
+          v[b] = *reinterpret_cast<const uint4*>(src);
+        } else {
+          __align__(16) __half tmp[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) tmp[e] = (k + e < p.IC) ? src[e] : __float2half(0.f);
+          v[b] = *reinterpret_cast<const uint4*>(tmp);
+        }
       }
     }
-    const __half2* h2 = reinterpret_cast<const __half2*>(&v);
-    float part = 0.f;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 f = __half22float2(h2[e]);
-      part += f.x + f.y;
-    }
+    for (int b = 0; b < kBatch; ++b) {
+      const __half2* h2 = reinterpret_cast<const __half2*>(&v[b]);
+      float part = 0.f;
 #pragma unroll
-    for (int o = 8; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);  // the 16 lanes of one (m, gl)
-    if (valid) {
-      uint4 o4 = interleave_pairs(v);
-      o4.y = hmul2(o4.y, 0x2C002C00u);
-      o4.w = hmul2(o4.w, 0x2C002C00u);
-      const int i = s & 3, t = s >> 2;
-      *reinterpret_cast<uint4*>(xs + static_cast<size_t>(m) * p.xs_stride + (gl * 16 + i * 4 + t) * 16) = o4;
-      if (s == 0) xsum[gl * mpad + m] = part;
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(h2[e]);
+        part += f.x + f.y;
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);  // the 16 lanes of one (m, gl)
+      if (cc[b] >= 0) {
+        const int gl = cc[b] >> 4, s = cc[b] & 15;  // s = 8-column block of the group, in source order
+        uint4 o4 = interleave_pairs(v[b]);
+        o4.y = hmul2(o4.y, 0x2C002C00u);
+        o4.w = hmul2(o4.w, 0x2C002C00u);
+        const int i = s & 3, t = s >> 2;
+        *reinterpret_cast<uint4*>(xs + static_cast<size_t>(mm[b]) * p.xs_stride + (gl * 16 + i * 4 + t) * 16) = o4;
+        if (s == 0) xsum[gl * mpad + mm[b]] = part;
+      }
     }
   }
 }
@@ -163,14 +162,21 @@ __device__ __forceinline__ bool mbar_wait_u32(uint32_t a, uint32_t parity, const
   uint32_t spins = 0;
   for (;;) {
     uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(a), "r"(parity), "r"(kSuspendHintNs)
-        : "memory");
+    if (cx.mode & 4) {
+      asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                   : "=r"(ok)
+                   : "r"(a), "r"(parity)
+                   : "memory");
+    } else {
+      asm volatile(
+          "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(ok)
+          : "r"(a), "r"(parity), "r"((cx.mode & 8) ? 20u : kSuspendHintNs)
+          : "memory");
+    }
     if (ok) return true;
     if ((++spins & 15u) == 0 && *cx.abort_flag) return false;
-    if (spins > kMbarSpinLimit) {
+    if (spins > ((cx.mode & 12) ? (kMbarSpinLimit << 6) : kMbarSpinLimit)) {
       *cx.abort_flag = 1;
       atomicExch(cx.status, 2u);
       return false;
@@ -199,49 +205,22 @@ __device__ __forceinline__ void cross_warp_reduce(float (&acc)[NB][4], float* re
   consumer_sync();
 }
 
-// Combine K-slice partial tiles: every slice stores its tile; the last arrival sums all slices in slice
-// order (deterministic) and returns true with the sum in fin.
-template <int NB>
-__device__ __forceinline__ bool splitk_combine(float* fin, float* partial_base, uint32_t* ctr, int slices, int ks,
-                                               volatile int* s_flag) {
-  constexpr int kElems = NB * 128;
-  float* mine = partial_base + static_cast<size_t>(ks) * kElems;
-  for (int e = threadIdx.x; e < kElems; e += kConsumerThreads) mine[e] = fin[e];
-  __threadfence();
-  consumer_sync();
-  if (threadIdx.x == 0) {
-    const uint32_t old = atomicAdd(ctr, 1u);
-    *s_flag = (old == static_cast<uint32_t>(slices - 1));
-  }
-  consumer_sync();
-  const bool last = (*s_flag != 0);
-  if (last) {
-    __threadfence();
-    for (int e = threadIdx.x; e < kElems; e += kConsumerThreads) {
-      float s = 0.f;
-      for (int k = 0; k < slices; ++k) s += ldg_cg_f32(partial_base + static_cast<size_t>(k) * kElems + e);
-      fin[e] = s;
-    }
-    if (threadIdx.x == 0) *ctr = 0u;  // ready for the next launch that uses this workspace
-  }
-  consumer_sync();
-  return last;
-}
-
-// One R unit: rows [16 rt, 16 rt + 16) of R times the columns of K slice ks (8 groups), tokens 0..M-1.
+// One R unit: rows [16 rt, 16 rt + 16) of R times the columns of K slice ks (gpr groups), tokens 0..M-1.  The
+// fp32 result goes to the unit's own slot of r_partial and the release counter is bumped; whoever needs r adds
+// the SKr slots of an R tile in slot order (so every reader, and r_buf, see the same bits).
 template <int NT>
-__device__ __forceinline__ void r_unit(const GemvParams& p, int unit, float* red, float* fin, volatile int* s_flag) {
+__device__ __forceinline__ void r_unit(const GemvParams& p, int unit, float* red, float* fin) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int rt = unit / p.SKr, ks = unit - rt * p.SKr;
   const int j0 = rt * kRTileRows;
-  const int gbase = ks * kChunkGroups, ng = min(kChunkGroups, p.G - gbase);
+  const int gbase = ks * p.gpr, ng = min(p.gpr, p.G - gbase);
   const __half* rowA = p.R + static_cast<size_t>(min(j0 + g, p.rank - 1)) * p.R_stride;
   const __half* rowB = p.R + static_cast<size_t>(min(j0 + g + 8, p.rank - 1)) * p.R_stride;
   float acc[NT][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-  if (warp < ng) {
-    const int kb = (gbase + warp) * kGroup + 32 * t;
+  for (int gl = warp; gl < ng; gl += kConsumerWarps) {
+    const int kb = (gbase + gl) * kGroup + 32 * t;
     uint4 a[4], b[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -273,20 +252,46 @@ __device__ __forceinline__ void r_unit(const GemvParams& p, int unit, float* red
       }
     }
   }
-  cross_warp_reduce<NT>(acc, red, fin);
-  bool finalize = true;
-  if (p.SKr > 1)
-    finalize = splitk_combine<NT>(fin, p.r_partial + static_cast<size_t>(rt) * p.SKr * (NT * 128), p.r_tile_ctr + rt,
-                                  p.SKr, ks, s_flag);
-  if (finalize) {
-    for (int e = threadIdx.x; e < p.M * 16; e += kConsumerThreads) {
-      const int tok = e >> 4, r = e & 15;
-      if (j0 + r < p.rank)
-        p.r_buf[static_cast<size_t>(tok) * p.rank + j0 + r] = __float2half_rn(fin[(tok >> 3) * 128 + (tok & 7) * 16 + r]);
+  cross_warp_reduce<NT>(acc, red, fin);  // fin[nt*128 + tok8*16 + row16]
+  float* slot = p.r_partial + static_cast<size_t>(unit) * (NT * 128);
+  for (int e = threadIdx.x; e < NT * 128; e += kConsumerThreads) slot[e] = fin[e];
+  __threadfence();
+  consumer_sync();
+  if (threadIdx.x == 0) atomicAdd(p.ws_head + WS_R_DONE, 1u);
+}
+
+// Eight consecutive elements r[tok][j .. j+8) (j a multiple of 8) as four half2 registers: the SKr fp32 slots of
+// the R tile added in slot order, then rounded to fp16.
+template <int NT>
+__device__ __forceinline__ uint4 r_frag_from_partials(const GemvParams& p, int tok, int j) {
+  const int rt = j >> 4, nt = tok >> 3;
+  const float* base = p.r_partial + (static_cast<size_t>(rt) * p.SKr * NT + nt) * 128 + (tok & 7) * 16 + (j & 15);
+  float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+  for (int ks = 0; ks < p.SKr; ++ks) {
+    const float4 q0 = __ldcg(reinterpret_cast<const float4*>(base + static_cast<size_t>(ks) * (NT * 128)));
+    const float4 q1 = __ldcg(reinterpret_cast<const float4*>(base + static_cast<size_t>(ks) * (NT * 128) + 4));
+    lo.x += q0.x; lo.y += q0.y; lo.z += q0.z; lo.w += q0.w;
+    hi.x += q1.x; hi.y += q1.y; hi.z += q1.z; hi.w += q1.w;
+  }
+  uint4 out;
+  __half2 h;
+  h = __floats2half2_rn(lo.x, lo.y); out.x = *reinterpret_cast<uint32_t*>(&h);
+  h = __floats2half2_rn(lo.z, lo.w); out.y = *reinterpret_cast<uint32_t*>(&h);
+  h = __floats2half2_rn(hi.x, hi.y); out.z = *reinterpret_cast<uint32_t*>(&h);
+  h = __floats2half2_rn(hi.z, hi.w); out.w = *reinterpret_cast<uint32_t*>(&h);
+  return out;
+}
+
+// Bounded wait until every R unit of this launch has published its slot.
+__device__ __forceinline__ void wait_r_done(const GemvParams& p, volatile int* abort_flag) {
+  uint32_t spins = 0;
+  while (ld_acquire_u32(p.ws_head + WS_R_DONE) < static_cast<uint32_t>(p.n_r_units)) {
+    __nanosleep(64);
+    if (*abort_flag || ++spins > kSpinLimit) {
+      *abort_flag = 1;
+      atomicExch(p.ws_head + WS_STATUS, 1u);
+      break;
     }
-    __threadfence();
-    consumer_sync();
-    if (threadIdx.x == 0) atomicAdd(p.ws_head + WS_R_DONE, 1u);
   }
 }
 
@@ -310,7 +315,7 @@ template <int NT>
 __global__ void __launch_bounds__(kGemvThreads, (NT <= 2) ? 2 : 1)
 gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__ TensorMaps tm) {
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ int s_abort, s_flag, s_ticket;
+  __shared__ int s_abort;
   constexpr int RT = kRowTiles;
   constexpr int NB = RT * NT;  // 16-row x 8-token fragment blocks per tile
 
@@ -319,12 +324,13 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint64_t* meta_full = empty_bar + kMaxStages;
   uint64_t* meta_empty = meta_full + kMetaDepth;
+  uint64_t* red_empty = meta_empty + kMetaDepth;     // [2]: the aux warp has drained a reduction buffer
   unsigned char* ring = smem + 256;
   const int meta_bytes = kTileRows * (p.meta_gp * 2 + p.meta_gw * 4);
   unsigned char* meta = ring + static_cast<size_t>(p.stages) * kStageBytes;
   float* red = reinterpret_cast<float*>(meta + static_cast<size_t>(kMetaDepth) * meta_bytes);
-  float* fin = red + kConsumerWarps * NB * 128;
-  float* xsum = fin + NB * 128;                      // [groups of the slice][8 NT]
+  float* fin = red + 2 * kConsumerWarps * NB * 128;  // red is double-buffered; fin serves the R units only
+  float* xsum = fin + NT * 128;                      // [groups of the slice][8 NT]
   unsigned char* xs = reinterpret_cast<unsigned char*>(xsum + p.gps * (8 * NT));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -347,12 +353,15 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       mbar_init(meta_full + i, 32);
       mbar_init(meta_empty + i, kConsumerWarps);
     }
+    mbar_init(red_empty + 0, 1);
+    mbar_init(red_empty + 1, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  Ctx cx{&s_abort, p.ws_head + WS_STATUS};
+  Ctx cx{&s_abort, p.ws_head + WS_STATUS, p.debug};
   const uint32_t full_u32 = smem_u32(full_bar), empty_u32 = smem_u32(empty_bar);
   const uint32_t mfull_u32 = smem_u32(meta_full), mempty_u32 = smem_u32(meta_empty);
+  const uint32_t rempty_u32 = smem_u32(red_empty);
 
   if (warp == kConsumerWarps) {
     // ================================================================ weight / L copy warp
@@ -404,34 +413,120 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       }
     }
   } else if (warp == kConsumerWarps + 1) {
-    // ================================================================ metadata warp: lane r fetches row r
-    uint32_t slot = 0, ph = 0;
+    // ================================================================ aux warp: metadata prefetch + tile epilogues
+    // Lane r fetches row r's scales / zero words a few tiles ahead with asynchronous 4-byte copies (the warp
+    // never waits for its own loads).  Between prefetches it finishes tiles: once the eight consumer warps have
+    // parked their partial sums in a reduction buffer (named barrier 2 + buf) it adds them up, runs the split-K
+    // combine, bias and the store, and hands the buffer back.  Consumers therefore never wait for one another.
+    uint32_t slot = 0, ph = 0, buf = 0;
+    int issued = 0, done = 0;
+    int tile_m = first_tile;
     bool ok = true;
-    for (int tile = first_tile; tile < p.n_tiles && ok; tile += tile_step) {
+    for (int tile = first_tile; tile < p.n_tiles; tile += tile_step) {
+      while (ok && tile_m < p.n_tiles && issued - done < kMetaDepth) {
+        const TileInfo tm_i = tile_info(p, tile_m, slice);
+        const MemberDev& mbm = p.mem[tm_i.mi];
+        if (!(ok = mbar_wait_u32(mempty_u32 + slot * 8, ph ^ 1, cx))) break;
+        const int row = min(tm_i.row0 + lane, mbm.OC - 1);
+        unsigned char* mbase = meta + static_cast<size_t>(slot) * meta_bytes;
+        __half* ms = reinterpret_cast<__half*>(mbase) + lane * p.meta_gp;
+        uint32_t* mz = reinterpret_cast<uint32_t*>(mbase + kTileRows * p.meta_gp * 2) + lane * p.meta_gw;
+        const __half* srow = mbm.scales + static_cast<size_t>(row) * mbm.sstride + g0;
+        if (((mbm.sstride | g0) & 1) == 0 && ((reinterpret_cast<uintptr_t>(mbm.scales) & 3) == 0)) {
+          const int np_full = ng >> 1;
+          for (int pi = 0; pi < np_full; ++pi) cp_async4(ms + 2 * pi, srow + 2 * pi);
+          if (ng & 1) ms[ng - 1] = srow[ng - 1];  // odd tail: there may be no 4 readable bytes at the end of a row
+        } else {
+          for (int gl = 0; gl < ng; ++gl) ms[gl] = srow[gl];
+        }
+        const int32_t* zrow = mbm.qzeros + static_cast<size_t>(row) * mbm.zstride + (g0 >> 3);
+        const int nw = (ng + 7) >> 3;
+        for (int wi = 0; wi < nw; ++wi) cp_async4(mz + wi, zrow + wi);
+        cp_async_mbar_arrive(meta_full + slot);
+        if (++slot == kMetaDepth) {
+          slot = 0;
+          ph ^= 1;
+        }
+        ++issued;
+        tile_m += tile_step;
+      }
+
+      // ---- epilogue of `tile`
       const TileInfo ti = tile_info(p, tile, slice);
       const MemberDev& mb = p.mem[ti.mi];
-      if (!(ok = mbar_wait_u32(mempty_u32 + slot * 8, ph ^ 1, cx))) break;
-      const int row = min(ti.row0 + lane, mb.OC - 1);
-      unsigned char* mbase = meta + static_cast<size_t>(slot) * meta_bytes;
-      __half* ms = reinterpret_cast<__half*>(mbase) + lane * p.meta_gp;
-      uint32_t* mz = reinterpret_cast<uint32_t*>(mbase + kTileRows * p.meta_gp * 2) + lane * p.meta_gw;
-      const __half* srow = mb.scales + static_cast<size_t>(row) * mb.sstride + g0;
-      // Asynchronous 4-byte copies: the warp never waits for its own loads, so several tiles of metadata are in
-      // flight at once (a synchronous load/store loop here costs a DRAM round trip per tile and throttles the CTA).
-      if (((mb.sstride | g0) & 1) == 0 && ((reinterpret_cast<uintptr_t>(mb.scales) & 3) == 0)) {
-        const int np_full = ng >> 1;
-        for (int pi = 0; pi < np_full; ++pi) cp_async4(ms + 2 * pi, srow + 2 * pi);
-        if (ng & 1) ms[ng - 1] = srow[ng - 1];  // odd tail: there may be no 4 readable bytes at the end of a row
-      } else {
-        for (int gl = 0; gl < ng; ++gl) ms[gl] = srow[gl];
+      if (buf == 0)
+        asm volatile("bar.sync 2, %0;" ::"n"(kConsumerThreads + 32) : "memory");
+      else
+        asm volatile("bar.sync 3, %0;" ::"n"(kConsumerThreads + 32) : "memory");
+      const float4* red4 = reinterpret_cast<const float4*>(red) + static_cast<size_t>(buf) * kConsumerWarps * NB * 32;
+      float4 v[NB];
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        v[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) {
+          const float4 q = red4[(w * NB + b) * 32 + lane];
+          v[b].x += q.x;
+          v[b].y += q.y;
+          v[b].z += q.z;
+          v[b].w += q.w;
+        }
       }
-      const int32_t* zrow = mb.qzeros + static_cast<size_t>(row) * mb.zstride + (g0 >> 3);
-      const int nw = (ng + 7) >> 3;
-      for (int wi = 0; wi < nw; ++wi) cp_async4(mz + wi, zrow + wi);
-      cp_async_mbar_arrive(meta_full + slot);
-      if (++slot == kMetaDepth) {
-        slot = 0;
-        ph ^= 1;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(red_empty + buf);  // the consumers may refill this buffer
+      buf ^= 1;
+      ++done;
+      bool finalize = true;
+      if (p.SK > 1) {
+        // every K slice parks its tile; the last slice to arrive adds them up in slice order (deterministic)
+        float4* part = reinterpret_cast<float4*>(p.sk_partial + static_cast<size_t>(tile) * p.SK * (NB * 128));
+#pragma unroll
+        for (int b = 0; b < NB; ++b) part[static_cast<size_t>(slice) * (NB * 32) + b * 32 + lane] = v[b];
+        __threadfence();
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) last = (atomicAdd(p.tile_ctr + tile, 1u) == static_cast<uint32_t>(p.SK - 1));
+        last = __shfl_sync(0xffffffffu, last, 0);
+        finalize = (last != 0);
+        if (finalize) {
+          __threadfence();
+#pragma unroll
+          for (int b = 0; b < NB; ++b) {
+            float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int k = 0; k < p.SK; ++k) {
+              const float4 q = __ldcg(part + static_cast<size_t>(k) * (NB * 32) + b * 32 + lane);
+              s4.x += q.x;
+              s4.y += q.y;
+              s4.z += q.z;
+              s4.w += q.w;
+            }
+            v[b] = s4;
+          }
+          if (lane == 0) p.tile_ctr[tile] = 0u;  // ready for the next launch that uses this workspace
+        }
+      }
+      if (finalize) {
+        // fragment block b = j * NT + nt; this lane holds rows (g, g+8) of row tile j for tokens 8 nt + 2t, +1
+        const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          const int j = b / NT, nt = b - j * NT;
+          const float vals[4] = {v[b].x, v[b].y, v[b].z, v[b].w};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int row = ti.row0 + j * 16 + g + ((c & 2) ? 8 : 0);
+            const int tok = nt * 8 + 2 * t + (c & 1);
+            if (row < mb.OC && tok < p.M) {
+              float o = vals[c];
+              if (mb.bias) o += __half2float(mb.bias[row]);
+              const size_t idx = static_cast<size_t>(tok) * mb.out_stride + row;
+              if (p.out_fp32)
+                static_cast<float*>(mb.out)[idx] = o;
+              else
+                static_cast<__half*>(mb.out)[idx] = __float2half_rn(o);
+            }
+          }
+        }
       }
     }
     asm volatile("cp.async.wait_all;" ::: "memory");  // nothing of this warp is in flight when the CTA retires
@@ -439,17 +534,13 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     // ================================================================ consumer warps
     const int g = lane >> 2, t = lane & 3;
     stage_x(p, g0, ng, xs, xsum, 8 * NT);
+    consumer_sync();  // publishes xs / xsum
     if (p.r_mode == 1) {
-      for (;;) {
-        consumer_sync();  // also orders s_ticket reuse and, first time round, publishes xs
-        if (threadIdx.x == 0) s_ticket = static_cast<int>(atomicAdd(p.ws_head + WS_TICKET, 1u));
-        consumer_sync();
-        const int u = s_ticket;
-        if (u >= p.n_r_units) break;
-        r_unit<NT>(p, u, red, fin, &s_flag);
-      }
+      // R units are dealt from the last CTA downwards (those CTAs hold the fewest row tiles).  The grid is
+      // persistent - never larger than what is resident at once - so every unit's owner is running.
+      for (int u = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x); u < p.n_r_units; u += gridDim.x)
+        r_unit<NT>(p, u, red, fin);
     }
-    consumer_sync();
 
     // per-lane constant shared addresses: weight quad (warp's group, lane's 16 B, lane's row), x chunk, x sums
     const uint32_t ring_lane = smem_u32(ring) + warp * 64 + t * 16 + g * kRowPitch;
@@ -462,7 +553,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) tokv[nt] = (nt * 8 + g) < p.M;
 
-    uint32_t st = 0, ph = 0, slot = 0, mph = 0;
+    uint32_t st = 0, ph = 0, slot = 0, mph = 0, rbuf = 0, rph = 0;
     bool ok = true, r_ready = (p.r_mode != 1);
     for (int tile = first_tile; tile < p.n_tiles; tile += tile_step) {
       const TileInfo ti = tile_info(p, tile, slice);
@@ -544,17 +635,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
 
       if (ti.corr) {
         if (!r_ready) {  // r comes from R units of this launch: bounded wait on the release counter
-          if (lane == 0) {
-            uint32_t spins = 0;
-            while (ld_acquire_u32(p.ws_head + WS_R_DONE) < static_cast<uint32_t>(p.n_r_tiles)) {
-              __nanosleep(100);
-              if (s_abort || ++spins > kSpinLimit) {
-                s_abort = 1;
-                atomicExch(p.ws_head + WS_STATUS, 1u);
-                break;
-              }
-            }
-          }
+          if (lane == 0) wait_r_done(p, &s_abort);
           __syncwarp();
           r_ready = true;
         }
@@ -572,8 +653,9 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
             uint4 rb[NT];
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
-              rb[nt] = (kin && tokv[nt]) ? ldg_cg_v4(p.r_buf + static_cast<size_t>(nt * 8 + g) * p.rank + 256 * l + k)
-                                         : make_uint4(0, 0, 0, 0);
+              rb[nt] = !(kin && tokv[nt]) ? make_uint4(0, 0, 0, 0)
+                       : (p.r_mode == 1)     ? r_frag_from_partials<NT>(p, nt * 8 + g, 256 * l + k)
+                                             : ldg_cg_v4(p.r_buf + static_cast<size_t>(nt * 8 + g) * p.rank + 256 * l + k);
 #pragma unroll
             for (int j = 0; j < RT; ++j) {
               const uint4 la = kin ? lds128(lbase + (j * 16) * lpitch) : make_uint4(0, 0, 0, 0);
@@ -604,25 +686,29 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
         mph ^= 1;
       }
 
-      cross_warp_reduce<NB>(acc, red, fin);
-      bool finalize = true;
-      if (p.SK > 1)
-        finalize = splitk_combine<NB>(fin, p.sk_partial + static_cast<size_t>(tile) * p.SK * (NB * 128), p.tile_ctr + tile,
-                                      p.SK, slice, &s_flag);
-      if (finalize) {
-        // fin[(j*NT + nt)*128 + tok8*16 + r]: row = row0 + 16 j + r, token = 8 nt + tok8
-        for (int e = threadIdx.x; e < p.M * kTileRows; e += kConsumerThreads) {
-          const int tok = e / kTileRows, rr = e - tok * kTileRows, row = ti.row0 + rr;
-          if (row < mb.OC) {
-            float v = fin[((rr >> 4) * NT + (tok >> 3)) * 128 + (tok & 7) * 16 + (rr & 15)];
-            if (mb.bias) v += __half2float(mb.bias[row]);
-            const size_t o = static_cast<size_t>(tok) * mb.out_stride + row;
-            if (p.out_fp32)
-              static_cast<float*>(mb.out)[o] = v;
-            else
-              static_cast<__half*>(mb.out)[o] = __float2half_rn(v);
-          }
-        }
+      // park the partial sums for the aux warp and move on to the next tile
+      ok = ok && mbar_wait_u32(rempty_u32 + rbuf * 8, rph ^ 1, cx);
+      {
+        float4* red4 = reinterpret_cast<float4*>(red) + static_cast<size_t>(rbuf) * kConsumerWarps * NB * 32;
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+          red4[(warp * NB + b) * 32 + lane] = make_float4(acc[b][0], acc[b][1], acc[b][2], acc[b][3]);
+      }
+      if (rbuf == 0)
+        asm volatile("bar.arrive 2, %0;" ::"n"(kConsumerThreads + 32) : "memory");
+      else
+        asm volatile("bar.arrive 3, %0;" ::"n"(kConsumerThreads + 32) : "memory");
+      if ((rbuf ^= 1) == 0) rph ^= 1;
+    }
+
+    // The CTA that ran R unit 0 leaves r in r_buf (fp16) for later launches of the group that load it.
+    if (p.r_mode == 1 && blockIdx.x == gridDim.x - 1) {
+      if (threadIdx.x == 0) wait_r_done(p, &s_abort);
+      consumer_sync();
+      for (int e = threadIdx.x; e < p.M * (p.n_r_tiles * 2); e += kConsumerThreads) {
+        const int tok = e / (p.n_r_tiles * 2), j = (e - tok * (p.n_r_tiles * 2)) * 8;
+        if (j < p.rank)  // rank is a multiple of 8
+          *reinterpret_cast<uint4*>(p.r_buf + static_cast<size_t>(tok) * p.rank + j) = r_frag_from_partials<NT>(p, tok, j);
       }
     }
   }
@@ -631,7 +717,6 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   if (p.r_mode == 1 && threadIdx.x == 0) {
     const uint32_t old = atomicAdd(p.ws_head + WS_EXIT, 1u);
     if (old == gridDim.x - 1) {  // last CTA out re-arms the counters for the next launch
-      p.ws_head[WS_TICKET] = 0u;
       p.ws_head[WS_R_DONE] = 0u;
       p.ws_head[WS_EXIT] = 0u;
       __threadfence();
@@ -707,7 +792,7 @@ size_t gemv_smem_bytes(const GemvParams& p, int NT) {
   size_t off = 256;
   off += static_cast<size_t>(p.stages) * kStageBytes;
   off += static_cast<size_t>(kMetaDepth) * kTileRows * (p.meta_gp * 2 + p.meta_gw * 4);
-  off += static_cast<size_t>(kConsumerWarps + 1) * kRowTiles * NT * 512;
+  off += static_cast<size_t>(2 * kConsumerWarps) * kRowTiles * NT * 512 + static_cast<size_t>(NT) * 512;
   off += static_cast<size_t>(p.gps) * NT * 32;
   off += static_cast<size_t>(p.M) * p.xs_stride;
   return off;

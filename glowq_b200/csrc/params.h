@@ -50,13 +50,12 @@ struct GemvParams {
   const __half* R;
   __half* r_buf;
   uint32_t* ws_head;      // header words
-  uint32_t* r_tile_ctr;   // [n_r_tiles] arrival counters of the r partial sums
-  float* r_partial;       // [n_r_tiles][SKr][NT*128]
+  float* r_partial;       // [n_r_tiles][SKr][NT*128] fp32 partial products of r, one slot per R unit
   uint32_t* tile_ctr;     // [n_tiles] arrival counters of the split-K partial sums
   float* sk_partial;      // [n_tiles][SK][kRowTiles*NT*128]
   int M, IC, x_stride, R_stride, G, rank, r_mode, out_fp32, n_members;
   int n_tiles, SK, gps;          // main work: tiles x K slices, groups per slice (multiple of kChunkGroups)
-  int n_r_tiles, SKr;            // r work: 16-row tiles of R x K slices of kChunkGroups groups
+  int n_r_tiles, SKr, gpr;       // r work: 16-row tiles of R x SKr K slices of gpr groups each
   int n_r_units;                 // n_r_tiles * SKr (0 unless r_mode == COMPUTE)
   int x_vec_ok;                  // x rows are 16-byte aligned
   int xs_stride;                 // bytes between tokens of the staged x slice in shared memory
