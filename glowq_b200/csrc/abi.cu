@@ -487,6 +487,65 @@ int glowq_w4a16_gemm_forward(const void* x, const int32_t* qweight, const void* 
   return glowq_w4a16_group_forward(&g);
 }
 
+}  // extern "C"
+
+// ---------------------------------------------------------------- scratch that is part of the library image
+// One array per device context, zero at load time.  Host code must not pass `g_static_scratch` itself to a
+// kernel - in host code the name is only a handle for cudaGetSymbolAddress - so the device address is looked
+// up once per device (with that device current) and cached.
+static __device__ __align__(256) unsigned char g_static_scratch[GLOWQ_W4A16_STATIC_SCRATCH_BYTES];
+
+namespace {
+void* g_static_scratch_addr[64] = {};
+std::mutex g_static_scratch_mutex;
+
+int static_scratch_address(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail_cuda(e);
+  if (dev < 0 || dev >= 64) return GLOWQ_ERR_UNSUPPORTED_DEVICE;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (!g_static_scratch_addr[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess) return fail_cuda(e);
+    if (!ptr) return GLOWQ_ERR_CUDA;
+    g_static_scratch_addr[dev] = ptr;
+  }
+  *out = g_static_scratch_addr[dev];
+  return GLOWQ_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int glowq_w4a16_gemv_forward_static(const void* x, const int32_t* qweight, const void* scales, const int32_t* qzeros,
+                                    void* out, int M, int IC, int OC, int group_size, int weight_stride_i32,
+                                    int zero_stride_i32, int scale_stride, void* stream) {
+  if (M < 0 || IC <= 0 || OC <= 0) return GLOWQ_ERR_BAD_ARGUMENT;
+  if (group_size <= 0 || group_size % 8 != 0) return GLOWQ_ERR_BAD_GROUP_SIZE;
+  const DeviceInfo* dev = nullptr;
+  int rc = device_info(&dev);
+  if (rc != GLOWQ_OK) return rc;
+  // The scratch this launch would use, from the same planner the launch itself runs.
+  const int n_tiles = ceil_div(OC, kTileRows);
+  const GemvPlan pl = make_plan(std::max(M, 1), IC, n_tiles, 0, dev->sms, 0);
+  if (pl.total > GLOWQ_W4A16_STATIC_SCRATCH_BYTES) return GLOWQ_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  rc = static_scratch_address(&scratch);
+  if (rc != GLOWQ_OK) return rc;
+  if (M == 0) return GLOWQ_OK;
+  // Counters must start at zero whatever an earlier (possibly failed) call left behind; partial sums are
+  // always written before they are read and need no clearing.
+  cudaError_t e = cudaMemsetAsync(scratch, 0, pl.off_r_partial, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail_cuda(e);
+  glowq_w4a16_group_t g;
+  fill_plain(g, x, qweight, scales, qzeros, out, M, IC, OC, group_size, weight_stride_i32, zero_stride_i32, scale_stride,
+             scratch, GLOWQ_W4A16_STATIC_SCRATCH_BYTES, stream);
+  g.kernel = GLOWQ_KERNEL_GEMV;
+  return glowq_w4a16_group_forward(&g);
+}
+
 int glowq_w4a16_group_forward_host(const glowq_w4a16_group_t* group, const void* x_host, void* const* out_host) {
   if (!group || !x_host || !out_host) return GLOWQ_ERR_BAD_ARGUMENT;
   const glowq_w4a16_group_t& g = *group;

@@ -148,6 +148,26 @@ int glowq_w4a16_group_forward_many(const glowq_w4a16_group_t* groups, int n);
  * (src/step3_eval_dataset.py:1047-1050). */
 int glowq_w4a16_group_forward_host(const glowq_w4a16_group_t* group, const void* x_host, void* const* out_host);
 
+/* Plain W4A16 product like glowq_w4a16_gemv_forward, for callers that cannot hand over a scratch buffer.
+ * This entry point has no counterpart in the reference.
+ *
+ * Some hosts may not allocate device memory on our behalf and cannot size or own a workspace either: a plug-in
+ * that only ever receives input and output pointers from its host, a serving loop whose memory plan was frozen
+ * before the first request, code that must not touch the CUDA allocator between steps.  For them the scratch
+ * (tile counters and split-K partial sums) lives in one array that is part of the library image itself,
+ * GLOWQ_W4A16_STATIC_SCRATCH_BYTES large; every GPU that loads the library carries it until the process exits.
+ * Calls whose launch plan needs more scratch than that return GLOWQ_ERR_TOO_LARGE and launch nothing.
+ *
+ * The first call on each device looks up the array's device address (with that device current); make that
+ * first call outside any stream capture.  All calls on a device share the one array: the kernels leave their
+ * counters at zero when they finish and this entry point re-zeroes the counter area on `stream` before every
+ * launch, but two calls that overlap on the GPU (different streams, no ordering between them) race on it.
+ * No cudaMalloc / cudaFree or other allocating routine is called. */
+#define GLOWQ_W4A16_STATIC_SCRATCH_BYTES (4u << 20)
+int glowq_w4a16_gemv_forward_static(const void* x, const int32_t* qweight, const void* scales, const int32_t* qzeros,
+                                    void* out, int M, int IC, int OC, int group_size, int weight_stride_i32,
+                                    int zero_stride_i32, int scale_stride, void* stream);
+
 /* Bytes of workspace a group call with these sizes needs (sync words + split-K partial sums). */
 size_t glowq_w4a16_workspace_bytes(int M, int IC, int OC_total, int rank, int n_members);
 
