@@ -26,6 +26,18 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
 using namespace glowq;
 
 namespace {
+int tensor_map_2d(CUtensorMap* out, CUtensorMapDataType dtype, const void* ptr, uint64_t dim0, uint64_t dim1,
+                  uint64_t stride_bytes, uint32_t box0, uint32_t box1, int swizzle128);
+}
+namespace glowq {
+// Shared with the GEMM translation unit: cached encode of a row-major 2-D tensor map.
+int tensor_map_2d_ex(CUtensorMap* out, CUtensorMapDataType dtype, const void* ptr, uint64_t dim0, uint64_t dim1,
+                     uint64_t stride_bytes, uint32_t box0, uint32_t box1, int swizzle128) {
+  return tensor_map_2d(out, dtype, ptr, dim0, dim1, stride_bytes, box0, box1, swizzle128);
+}
+}  // namespace glowq
+
+namespace {
 
 thread_local int t_last_cuda_error = 0;
 
@@ -79,10 +91,10 @@ EncodeTiledFn encode_tiled_fn() {
 struct MapKey {
   const void* ptr;
   uint64_t dim0, dim1, stride_bytes;
-  uint32_t box0, box1, dtype;
+  uint32_t box0, box1, dtype, swizzle;
   bool operator==(const MapKey& o) const {
     return ptr == o.ptr && dim0 == o.dim0 && dim1 == o.dim1 && stride_bytes == o.stride_bytes && box0 == o.box0 &&
-           box1 == o.box1 && dtype == o.dtype;
+           box1 == o.box1 && dtype == o.dtype && swizzle == o.swizzle;
   }
 };
 struct MapSlot {
@@ -96,12 +108,12 @@ std::mutex g_map_mutex;
 
 // Row-major 2-D tensor [dim1 rows, dim0 elements], row pitch stride_bytes, box [box1 rows, box0 elements].
 int tensor_map_2d(CUtensorMap* out, CUtensorMapDataType dtype, const void* ptr, uint64_t dim0, uint64_t dim1,
-                  uint64_t stride_bytes, uint32_t box0, uint32_t box1) {
+                  uint64_t stride_bytes, uint32_t box0, uint32_t box1, int swizzle128 = 0) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return GLOWQ_ERR_UNSUPPORTED_DEVICE;
-  const MapKey key{ptr, dim0, dim1, stride_bytes, box0, box1, static_cast<uint32_t>(dtype)};
+  const MapKey key{ptr, dim0, dim1, stride_bytes, box0, box1, static_cast<uint32_t>(dtype), static_cast<uint32_t>(swizzle128)};
   size_t h = reinterpret_cast<uintptr_t>(ptr) >> 8;
-  h = (h ^ (h >> 12) ^ (dim0 * 0x9E3779B97F4A7C15ull) ^ (dim1 << 7) ^ box0) % kMapCacheSlots;
+  h = (h ^ (h >> 12) ^ (dim0 * 0x9E3779B97F4A7C15ull) ^ (dim1 << 7) ^ box0 ^ (box1 << 3) ^ swizzle128) % kMapCacheSlots;
   std::lock_guard<std::mutex> lock(g_map_mutex);
   MapSlot& slot = g_map_cache[h];
   if (!(slot.valid && slot.key == key)) {
@@ -110,7 +122,8 @@ int tensor_map_2d(CUtensorMap* out, CUtensorMapDataType dtype, const void* ptr, 
     const cuuint32_t box[2] = {box0, box1};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = enc(&slot.map, dtype, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                           swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
       slot.valid = false;
       return GLOWQ_ERR_CUDA;

@@ -1,9 +1,480 @@
-// Tensor-core (tcgen05 / TMEM) corrected W4A16 GEMM for prefill token counts.
+// Tensor-core corrected W4A16 GEMM for prefill token counts (sm_100a: tcgen05.mma, TMEM accumulators, TMA).
+//
+//   Y[M, OC] = X[M, IC] . dequant(Q)^T  +  alpha * r[M, rank] . L[OC, rank]^T  (+ bias),     r = X . R^T
+//
+// One CTA computes a 256-token x 128-column block of Y as two 128x128 fp32 accumulators in tensor memory.
+// K runs through a 4-stage shared-memory ring in steps of 64:
+//   warp 0      TMA producer: the two 128x64 activation tiles (128-byte swizzle) and the 128 x 32 B packed
+//               int4 tile of the step; in the correction phase the r tiles and the L tile (fp16, swizzled, no
+//               dequantisation) - the correction is simply more K steps of the same pipeline.
+//   warps 2-5   dequantise: thread i turns row i of the packed tile into 64 fp16 values half_rn((code - zero) *
+//               scale) - the same exact-integer unpack + one HMUL2 as the stand-alone dequant kernel, so the
+//               shared-memory tile is bit-identical to the reference's dequantised weight - and stores them as
+//               row i of the K-major, 128-byte-swizzled B tile; afterwards they are the epilogue (TMEM -> registers
+//               -> bias / alpha -> global).
+//   warp 1      allocates tensor memory and issues tcgen05.mma (one elected lane): 2 accumulators x 4 k16 slices
+//               per step, then tcgen05.commit to release the stage.
+// The dequantised weight never goes to HBM (the reference writes and re-reads a full fp16 copy per call).
+// The same kernel with an fp16 B operand by TMA (no dequant warps' work) computes r = X . R^T.
+// Every mbarrier wait is bounded; on expiry a status word is set and the CTA drains and frees its tensor memory.
+#include <cstring>
+
 #include "../../include/glowq_w4a16.h"
+#include "common.cuh"
 #include "params.h"
 
 namespace glowq {
-bool gemm_supported(const glowq_w4a16_group_t&) { return false; }
-size_t gemm_workspace_bytes(int, int, int, int, int) { return 0; }
-int gemm_group_forward(const glowq_w4a16_group_t&, cudaStream_t, cudaError_t*) { return GLOWQ_ERR_UNSUPPORTED_SHAPE; }
+
+int tensor_map_2d_ex(CUtensorMap* out, CUtensorMapDataType dtype, const void* ptr, uint64_t dim0, uint64_t dim1,
+                     uint64_t stride_bytes, uint32_t box0, uint32_t box1, int swizzle128);
+
+namespace {
+
+constexpr int BM = 128;   // tokens per accumulator (MMA M)
+constexpr int MT = 2;     // accumulators per CTA
+constexpr int BN = 128;   // output columns per CTA (MMA N)
+constexpr int BK = 64;    // K per stage: 128 bytes of fp16 = one swizzle row
+constexpr int kStagesG = 4;
+constexpr int kABytes = BM * BK * 2;        // 16 KB
+constexpr int kBBytes = BN * BK * 2;        // 16 KB
+constexpr int kPBytes = BN * (BK / 8) * 4;  // 4 KB packed
+constexpr int kStageG = MT * kABytes + kBBytes + kPBytes;  // 53248
+constexpr int kGemmThreads = 192;
+constexpr int kGemmSmem = 2048 + kStagesG * kStageG;  // 1 KB of alignment slack + 1 KB of barriers + the ring
+constexpr uint32_t kGemmSpin = 1u << 18;
+constexpr uint32_t kTmemCols = 512;
+// instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = 128, M = 128
+constexpr uint32_t kIdesc = (1u << 4) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
+
+struct GemmParams {
+  const __half* scales;
+  const int32_t* qzeros;
+  const __half* bias;
+  void* out;
+  uint32_t* status;
+  int M, OC, nk1, nk2, w4, sstride, zstride, out_stride, out_fp32, lr_separate, out_vec_ok;
+  float alpha;
+};
+struct alignas(64) GemmMaps {
+  CUtensorMap a1, b1, a2, b2;  // phase 1: x, packed weight (or fp16 B); phase 2: r, L
+};
+
+__device__ __forceinline__ uint32_t sm_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void g_mbar_init(uint32_t a, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(count) : "memory");
+}
+__device__ __forceinline__ void g_mbar_arrive(uint32_t a) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(a) : "memory");
+}
+__device__ __forceinline__ void g_mbar_expect_tx(uint32_t a, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool g_mbar_wait(uint32_t a, uint32_t parity, volatile int* abort_flag, uint32_t* status) {
+  uint32_t spins = 0;
+  for (;;) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(a), "r"(parity)
+                 : "memory");
+    if (ok) return true;
+    if ((++spins & 63u) == 0 && *abort_flag) return false;
+    if (spins > kGemmSpin) {
+      *abort_flag = 1;
+      atomicExch(status, 3u);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void g_tma_2d(uint32_t dst, const CUtensorMap* tmap, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(tmap), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+// K-major, 128-byte-swizzled operand tile: rows of 128 B, 8-row atoms 1024 B apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(1) << 16) |
+         (static_cast<uint64_t>(1024 >> 4) << 32) | (static_cast<uint64_t>(1) << 46) | (static_cast<uint64_t>(2) << 61);
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+      "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
+        "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
+        "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ GemmMaps tm) {
+  extern __shared__ unsigned char smem[];
+  __shared__ int s_abort;
+  __shared__ uint32_t s_tmem_base;
+  const uint32_t smem0 = (sm_u32(smem) + 1023u) & ~1023u;  // swizzled operand tiles want 1024-byte alignment
+  // barriers live in the first 1 KB: full[4], empty[4], bready[4], accum
+  const uint32_t full_b = smem0, empty_b = smem0 + 64, bready_b = smem0 + 128, accum_b = smem0 + 192;
+  const uint32_t ring = smem0 + 1024;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * (BM * MT);
+  const int n_mt = (m0 + BM < p.M) ? 2 : 1;
+  const int nk = p.nk1 + p.nk2;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int i = 0; i < kStagesG; ++i) {
+      g_mbar_init(full_b + 8 * i, 1);
+      g_mbar_init(empty_b + 8 * i, 1);
+      g_mbar_init(bready_b + 8 * i, 4);
+    }
+    g_mbar_init(accum_b, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sm_u32(&s_tmem_base)), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = s_tmem_base;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp == 0) {
+    // ================================================================ TMA producer
+    uint32_t st = 0, ph = 0;
+    int issued = 0;
+    bool ok = true;
+    for (int it = 0; it < nk && ok; ++it) {
+      if (!(ok = g_mbar_wait(empty_b + 8 * st, ph ^ 1, abort_flag, p.status))) break;
+      if (lane == 0) {
+        const uint32_t sbase = ring + st * kStageG, bar = full_b + 8 * st;
+        const bool phase1 = it < p.nk1;
+        const int kk = phase1 ? it : it - p.nk1;
+        const bool packed = phase1 && p.w4;
+        g_mbar_expect_tx(bar, n_mt * kABytes + (packed ? kPBytes : kBBytes));
+        const CUtensorMap* ta = phase1 ? &tm.a1 : &tm.a2;
+        g_tma_2d(sbase, ta, kk * BK, m0, bar);
+        if (n_mt == 2) g_tma_2d(sbase + kABytes, ta, kk * BK, m0 + BM, bar);
+        if (packed)
+          g_tma_2d(sbase + MT * kABytes + kBBytes, &tm.b1, kk * (BK / 8), n0, bar);
+        else
+          g_tma_2d(sbase + MT * kABytes, phase1 ? &tm.b1 : &tm.b2, kk * BK, n0, bar);
+      }
+      ++issued;
+      if (++st == kStagesG) {
+        st = 0;
+        ph ^= 1;
+      }
+    }
+    if (!ok) {  // wait (bounded) for copies that are still in flight
+      for (int j = (issued > kStagesG ? issued - kStagesG : 0); j < issued; ++j) {
+        uint32_t spins = 0, done = 0;
+        while (!done && ++spins < kGemmSpin)
+          asm volatile(
+              "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+              : "=r"(done)
+              : "r"(full_b + 8 * (j % kStagesG)), "r"((j / kStagesG) & 1)
+              : "memory");
+      }
+    }
+  } else if (warp == 1) {
+    // ================================================================ MMA issuer
+    uint32_t st = 0, ph = 0;
+    bool ok = true;
+    for (int it = 0; it < nk; ++it) {
+      ok = ok && g_mbar_wait(full_b + 8 * st, ph, abort_flag, p.status);
+      ok = ok && g_mbar_wait(bready_b + 8 * st, ph, abort_flag, p.status);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (lane == 0) {
+        if (ok) {
+          const uint32_t sbase = ring + st * kStageG;
+          const bool phase2 = it >= p.nk1;
+          const uint32_t lr_off = (phase2 && p.lr_separate) ? BN : 0;
+          const bool first = phase2 ? (p.lr_separate && it == p.nk1) : (it == 0);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            if (mt < n_mt) {
+#pragma unroll
+              for (int k16 = 0; k16 < BK / 16; ++k16) {
+                const uint64_t ad = smem_desc_sw128(sbase + mt * kABytes + k16 * 32);
+                const uint64_t bd = smem_desc_sw128(sbase + MT * kABytes + k16 * 32);
+                umma_f16(tmem_base + mt * (2 * BN) + lr_off, ad, bd, (first && k16 == 0) ? 0u : 1u);
+              }
+            }
+          }
+        }
+        umma_commit(empty_b + 8 * st);  // the stage is free once the MMAs above have read it
+      }
+      __syncwarp();
+      if (++st == kStagesG) {
+        st = 0;
+        ph ^= 1;
+      }
+    }
+    if (lane == 0) umma_commit(accum_b);
+    __syncwarp();
+  } else {
+    // ================================================================ dequant warps, then epilogue
+    const int rloc = threadIdx.x - 64;  // row of the B tile
+    const int row = n0 + rloc;
+    const bool rvalid = row < p.OC;
+    const uint32_t b_row = (static_cast<uint32_t>(rloc) >> 3) * 1024 + (static_cast<uint32_t>(rloc) & 7) * 128;
+    const uint32_t sw = static_cast<uint32_t>(rloc) & 7;
+    uint32_t st = 0, ph = 0;
+    bool ok = true;
+    int cur_g = -1;
+    uint32_t s2 = 0, zlo = 0, zhi = 0;
+    for (int it = 0; it < nk; ++it) {
+      ok = ok && g_mbar_wait(empty_b + 8 * st, ph ^ 1, abort_flag, p.status);
+      if (it < p.nk1 && p.w4) {
+        const int G = it >> 1;  // 64-column steps, 128-column groups
+        if (G != cur_g) {
+          cur_g = G;
+          uint32_t sbits = 0, z = 0;
+          if (rvalid) {
+            sbits = __half_as_ushort(p.scales[static_cast<size_t>(row) * p.sstride + G]);
+            z = nibble(p.qzeros + static_cast<size_t>(row) * p.zstride, G);
+          }
+          s2 = sbits * 0x00010001u;
+          zero_consts(z, zlo, zhi);
+        }
+        ok = ok && g_mbar_wait(full_b + 8 * st, ph, abort_flag, p.status);
+        if (ok) {
+          const uint32_t sbase = ring + st * kStageG;
+          const uint32_t pbase = sbase + MT * kABytes + kBBytes + rloc * 32;
+          uint32_t w[8];
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(pbase));
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+                       : "r"(pbase + 16));
+          const uint32_t bbase = sbase + MT * kABytes + b_row;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {  // 16-byte chunk c = columns 8c .. 8c+7 of the step
+            uint32_t h[4];
+            unpack8_minus_zero(w[c], zlo, zhi, h);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) h[i] = hmul2(h[i], s2);  // (n0,n4) (n1,n5) (n2,n6) (n3,n7), rounded once
+            const uint32_t v0 = prmt(h[0], h[1], 0x5410), v1 = prmt(h[2], h[3], 0x5410);
+            const uint32_t v2 = prmt(h[0], h[1], 0x7632), v3 = prmt(h[2], h[3], 0x7632);
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bbase + ((static_cast<uint32_t>(c) ^ sw) << 4)), "r"(v0),
+                         "r"(v1), "r"(v2), "r"(v3)
+                         : "memory");
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the MMA
+        }
+      }
+      __syncwarp();
+      if (lane == 0) g_mbar_arrive(bready_b + 8 * st);
+      if (++st == kStagesG) {
+        st = 0;
+        ph ^= 1;
+      }
+    }
+
+    // ---- epilogue: this warp owns TMEM lanes 32 (warp % 4) .. +31 = 32 tokens; one token per lane
+    ok = ok && g_mbar_wait(accum_b, 0, abort_flag, p.status);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int q = warp & 3;
+    for (int mt = 0; mt < n_mt; ++mt) {
+      const int tok = m0 + mt * BM + q * 32 + lane;
+      for (int cb = 0; cb < BN / 32; ++cb) {
+        uint32_t acc[32], lr[32];
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mt * (2 * BN) + cb * 32;
+        tmem_ld32(taddr, acc);
+        if (p.lr_separate) tmem_ld32(taddr + BN, lr);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int c0 = n0 + cb * 32;
+        if (ok && tok < p.M) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = __uint_as_float(acc[j]);
+            if (p.lr_separate) v[j] = fmaf(p.alpha, __uint_as_float(lr[j]), v[j]);
+            if (p.bias && c0 + j < p.OC) v[j] += __half2float(p.bias[c0 + j]);
+          }
+          if (p.out_fp32) {
+            float* o = static_cast<float*>(p.out) + static_cast<size_t>(tok) * p.out_stride + c0;
+            if (p.out_vec_ok && c0 + 32 <= p.OC) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (c0 + j < p.OC) o[j] = v[j];
+            }
+          } else {
+            __half* o = static_cast<__half*>(p.out) + static_cast<size_t>(tok) * p.out_stride + c0;
+            if (p.out_vec_ok && c0 + 32 <= p.OC) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 pk;
+                __half2 h;
+                h = __floats2half2_rn(v[j], v[j + 1]);
+                pk.x = *reinterpret_cast<uint32_t*>(&h);
+                h = __floats2half2_rn(v[j + 2], v[j + 3]);
+                pk.y = *reinterpret_cast<uint32_t*>(&h);
+                h = __floats2half2_rn(v[j + 4], v[j + 5]);
+                pk.z = *reinterpret_cast<uint32_t*>(&h);
+                h = __floats2half2_rn(v[j + 6], v[j + 7]);
+                pk.w = *reinterpret_cast<uint32_t*>(&h);
+                *reinterpret_cast<uint4*>(o + j) = pk;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (c0 + j < p.OC) o[j] = __float2half_rn(v[j]);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline int cdiv(int a, int b) { return (a + b - 1) / b; }
+
+cudaError_t launch_gemm(const GemmParams& p, const GemmMaps& tm, cudaStream_t stream) {
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem);
+    if (e != cudaSuccess) return e;
+    attr_done[dev] = true;
+  }
+  dim3 grid(cdiv(p.OC, BN), cdiv(p.M, BM * MT));
+  gemm_w4a16_kernel<<<grid, kGemmThreads, kGemmSmem, stream>>>(p, tm);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool gemm_supported(const glowq_w4a16_group_t& g) {
+  if (g.group_size != kGroup || g.M < 1) return false;
+  if (!al16(g.x) || (g.x_stride & 7) || (g.IC & 7)) return false;
+  const int G = (g.IC + kGroup - 1) / kGroup;
+  for (int i = 0; i < g.n_members; ++i) {
+    const auto& m = g.members[i];
+    if (m.weight_stride_i32 < G * 16 || (m.weight_stride_i32 & 3) || !al16(m.qweight)) return false;
+    if (g.r_mode != GLOWQ_R_NONE && m.L && (!al16(m.L) || (m.L_stride & 7))) return false;
+  }
+  if (g.r_mode != GLOWQ_R_NONE && ((g.rank & 7) || !al16(g.r_buf))) return false;
+  if (g.r_mode == GLOWQ_R_COMPUTE && (!al16(g.R) || (g.R_stride & 7))) return false;
+  return true;
+}
+
+size_t gemm_workspace_bytes(int, int, int, int, int) { return kWsHeaderBytes; }
+
+int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaError_t* cuda_err) {
+  if (g.workspace_bytes < kWsHeaderBytes) return GLOWQ_ERR_WORKSPACE_TOO_SMALL;
+  uint32_t* status = static_cast<uint32_t*>(g.workspace) + WS_STATUS;
+  const int G = (g.IC + kGroup - 1) / kGroup;
+  const bool any_corr = [&] {
+    if (g.r_mode == GLOWQ_R_NONE) return false;
+    for (int i = 0; i < g.n_members; ++i)
+      if (g.members[i].L && g.members[i].alpha != 0.f) return true;
+    return false;
+  }();
+  auto map = [&](CUtensorMap* out, CUtensorMapDataType dt, const void* ptr, uint64_t d0, uint64_t d1, uint64_t stride,
+                 uint32_t b0, uint32_t b1, int sw) { return tensor_map_2d_ex(out, dt, ptr, d0, d1, stride, b0, b1, sw); };
+  int rc;
+  CUtensorMap tm_x;
+  if ((rc = map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.x, g.IC, g.M, static_cast<uint64_t>(g.x_stride) * 2, BK, BM, 1)))
+    return rc;
+
+  // r = X . R^T (fp16 B operand by TMA), once per group, into r_buf
+  if (g.r_mode == GLOWQ_R_COMPUTE) {
+    GemmParams p{};
+    GemmMaps tm;
+    std::memset(&tm, 0, sizeof(tm));
+    tm.a1 = tm_x;
+    if ((rc = map(&tm.b1, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.R, g.IC, g.rank, static_cast<uint64_t>(g.R_stride) * 2, BK, BN, 1)))
+      return rc;
+    tm.a2 = tm.a1;
+    tm.b2 = tm.b1;
+    p.status = status;
+    p.out = g.r_buf;
+    p.M = g.M;
+    p.OC = g.rank;
+    p.nk1 = cdiv(g.IC, BK);
+    p.nk2 = 0;
+    p.w4 = 0;
+    p.out_stride = g.rank;
+    p.out_fp32 = 0;
+    p.alpha = 1.f;
+    p.out_vec_ok = 1;  // rank % 8 == 0 and r_buf aligned
+    cudaError_t e = launch_gemm(p, tm, stream);
+    if (e != cudaSuccess) {
+      *cuda_err = e;
+      return GLOWQ_ERR_CUDA;
+    }
+  }
+  CUtensorMap tm_r;
+  std::memset(&tm_r, 0, sizeof(tm_r));
+  if (any_corr &&
+      (rc = map(&tm_r, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.r_buf, g.rank, g.M, static_cast<uint64_t>(g.rank) * 2, BK, BM, 1)))
+    return rc;
+
+  for (int i = 0; i < g.n_members; ++i) {
+    const auto& m = g.members[i];
+    const bool corr = g.r_mode != GLOWQ_R_NONE && m.L && m.alpha != 0.f;
+    GemmParams p{};
+    GemmMaps tm;
+    std::memset(&tm, 0, sizeof(tm));
+    tm.a1 = tm_x;
+    if ((rc = map(&tm.b1, CU_TENSOR_MAP_DATA_TYPE_INT32, m.qweight, static_cast<uint64_t>(G) * 16, m.OC,
+                  static_cast<uint64_t>(m.weight_stride_i32) * 4, BK / 8, BN, 0)))
+      return rc;
+    tm.a2 = corr ? tm_r : tm_x;
+    tm.b2 = tm.b1;
+    if (corr &&
+        (rc = map(&tm.b2, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, m.L, g.rank, m.OC, static_cast<uint64_t>(m.L_stride) * 2, BK, BN, 1)))
+      return rc;
+    p.scales = static_cast<const __half*>(m.scales);
+    p.qzeros = m.qzeros;
+    p.bias = static_cast<const __half*>(m.bias);
+    p.out = m.out;
+    p.status = status;
+    p.M = g.M;
+    p.OC = m.OC;
+    p.nk1 = cdiv(g.IC, BK);
+    p.nk2 = corr ? cdiv(g.rank, BK) : 0;
+    p.w4 = 1;
+    p.sstride = m.scale_stride;
+    p.zstride = m.zero_stride_i32;
+    p.out_stride = m.out_stride;
+    p.out_fp32 = g.out_dtype == GLOWQ_OUT_F32;
+    p.alpha = m.alpha;
+    p.lr_separate = corr && m.alpha != 1.f;
+    const int esz = p.out_fp32 ? 4 : 2;
+    p.out_vec_ok = al16(m.out) && ((static_cast<size_t>(m.out_stride) * esz) % 16 == 0);
+    cudaError_t e = launch_gemm(p, tm, stream);
+    if (e != cudaSuccess) {
+      *cuda_err = e;
+      return GLOWQ_ERR_CUDA;
+    }
+  }
+  return GLOWQ_OK;
+}
+
 }  // namespace glowq
