@@ -236,21 +236,27 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     const uint32_t sw = static_cast<uint32_t>(rloc) & 7;
     uint32_t st = 0, ph = 0;
     bool ok = true;
-    int cur_g = -1;
+    // scale / zero-point of this row: group G is needed at steps 2G and 2G+1; the next group's pair is fetched one
+    // group ahead so that the global-load latency never sits between a stage becoming free and its tile being written
+    const int n_groups = (p.nk1 + 1) >> 1;
+    auto fetch_sz = [&](int G, uint32_t& sbits, uint32_t& z) {
+      sbits = 0;
+      z = 0;
+      if (rvalid && G < n_groups && p.w4) {
+        sbits = __half_as_ushort(p.scales[static_cast<size_t>(row) * p.sstride + G]);
+        z = nibble(p.qzeros + static_cast<size_t>(row) * p.zstride, G);
+      }
+    };
+    uint32_t nx_s, nx_z;
+    fetch_sz(0, nx_s, nx_z);
     uint32_t s2 = 0, zlo = 0, zhi = 0;
     for (int it = 0; it < nk; ++it) {
       ok = ok && g_mbar_wait(empty_b + 8 * st, ph ^ 1, abort_flag, p.status);
       if (it < p.nk1 && p.w4) {
-        const int G = it >> 1;  // 64-column steps, 128-column groups
-        if (G != cur_g) {
-          cur_g = G;
-          uint32_t sbits = 0, z = 0;
-          if (rvalid) {
-            sbits = __half_as_ushort(p.scales[static_cast<size_t>(row) * p.sstride + G]);
-            z = nibble(p.qzeros + static_cast<size_t>(row) * p.zstride, G);
-          }
-          s2 = sbits * 0x00010001u;
-          zero_consts(z, zlo, zhi);
+        if ((it & 1) == 0) {  // first step of group it/2
+          s2 = nx_s * 0x00010001u;
+          zero_consts(nx_z, zlo, zhi);
+          fetch_sz((it >> 1) + 1, nx_s, nx_z);
         }
         ok = ok && g_mbar_wait(full_b + 8 * st, ph, abort_flag, p.status);
         if (ok) {

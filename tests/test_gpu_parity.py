@@ -209,6 +209,86 @@ def test_counters_rearm_over_many_launches():
     assert_close(out, lin.oracle(x, R))
 
 
+# ---------------------------------------------------------------------------------------------- tensor-core GEMM
+@pytest.mark.parametrize("M,oc,ic,rank,alpha,bias", [
+    (64, 256, 512, 0, 1.0, False), (128, 128, 128, 0, 1.0, False), (200, 136, 1152, 0, 1.0, True),
+    (257, 384, 1024, 64, 1.0, True), (300, 320, 1024, 40, 0.5, False), (1024, 1024, 3072, 128, 1.0, False),
+    (2048, 512, 5120, 256, 1.0, False), (70, 72, 136, 16, 2.0, True)])
+def test_gemm_parity(M, oc, ic, rank, alpha, bias):
+    rng = np.random.default_rng(M + oc + ic + rank)
+    lin = Linear(rng, oc, ic, rank=rank, bias=bias)
+    x = rng.standard_normal((M, ic)).astype(np.float16)
+    R = (rng.standard_normal((max(rank, 8), ic)) * 0.01).astype(np.float16)
+    for odt in (K.OUT_F16, K.OUT_F32):
+        out = new_out(M, lin, odt)
+        if rank:
+            r_buf = torch.zeros(M, rank, dtype=torch.float16, device="cuda")
+            g = make_group(dev(x), [lin], [out], R_d=dev(R), r_buf=r_buf, r_mode=K.R_COMPUTE, alpha=alpha,
+                           kernel=K.KERNEL_GEMM, out_dtype=odt)
+        else:
+            g = make_group(dev(x), [lin], [out], kernel=K.KERNEL_GEMM, out_dtype=odt)
+        assert run_group(g) == 0 and status_ok(g) == 0
+        assert_close(out, lin.oracle(x, R if rank else None, alpha=alpha), tag=f"gemm {M}x{oc}x{ic} r{rank}")
+        if rank:
+            r_want = x.astype(np.float32) @ R.astype(np.float32).T
+            assert np.abs(r_buf.float().cpu().numpy() - r_want).max() <= 4e-3
+
+
+def test_gemm_group_and_cache_modes():
+    """q computes r (one r product for the group), k and v load it; also the fused three-member call."""
+    rng = np.random.default_rng(12)
+    lins = [Linear(rng, 512, 2048, rank=64), Linear(rng, 128, 2048, rank=64, bias=True), Linear(rng, 128, 2048, rank=64)]
+    R = (rng.standard_normal((64, 2048)) * 0.01).astype(np.float16)
+    x = rng.standard_normal((384, 2048)).astype(np.float16)
+    x_d, R_d = dev(x), dev(R)
+    for fused in (True, False):
+        outs = [new_out(384, l) for l in lins]
+        r_buf = torch.zeros(384, 64, dtype=torch.float16, device="cuda")
+        if fused:
+            g = make_group(x_d, lins, outs, R_d=R_d, r_buf=r_buf, r_mode=K.R_COMPUTE, kernel=K.KERNEL_GEMM)
+            assert run_group(g) == 0 and status_ok(g) == 0
+        else:
+            for i, (l, o) in enumerate(zip(lins, outs)):
+                g = make_group(x_d, [l], [o], R_d=R_d, r_buf=r_buf, r_mode=K.R_COMPUTE if i == 0 else K.R_LOAD,
+                               kernel=K.KERNEL_GEMM)
+                assert run_group(g) == 0 and status_ok(g) == 0
+        for l, o in zip(lins, outs):
+            assert_close(o, l.oracle(x, R))
+
+
+def test_gemm_shared_memory_weight_tile_is_bit_exact():
+    """One-hot activations read the dequantised weight back through the tensor-core path: y[m, oc] = W[oc, m]
+    exactly (a single product with 1.0 per output), so the tile the MMA consumes is bit-identical to the reference
+    dequantisation."""
+    rng = np.random.default_rng(13)
+    for oc, ic in ((256, 512), (136, 256)):
+        lin = Linear(rng, oc, ic, w_std=0.05)
+        x = np.eye(ic, dtype=np.float16)
+        out = new_out(ic, lin)
+        g = make_group(dev(x), [lin], [out], kernel=K.KERNEL_GEMM)
+        assert run_group(g) == 0 and status_ok(g) == 0
+        want = O.dequant_full(lin.qweight, lin.qzeros, lin.scales, ic, 128)
+        np.testing.assert_array_equal(out.cpu().numpy().T.copy().view(np.uint16), want.view(np.uint16))
+
+
+def test_gemv_and_gemm_agree_at_the_switch_over():
+    rng = np.random.default_rng(14)
+    lin = Linear(rng, 640, 3072, rank=64)
+    R = (rng.standard_normal((64, 3072)) * 0.01).astype(np.float16)
+    for M in (32, 33, 64):
+        x = rng.standard_normal((M, 3072)).astype(np.float16)
+        ys = []
+        for kern in (K.KERNEL_GEMV, K.KERNEL_GEMM, K.KERNEL_AUTO):
+            out = new_out(M, lin, K.OUT_F32)
+            r_buf = torch.zeros(M, 64, dtype=torch.float16, device="cuda")
+            g = make_group(dev(x), [lin], [out], R_d=dev(R), r_buf=r_buf, r_mode=K.R_COMPUTE, kernel=kern,
+                           out_dtype=K.OUT_F32)
+            assert run_group(g) == 0 and status_ok(g) == 0
+            ys.append(out.cpu().numpy())
+            assert_close(out, lin.oracle(x, R), tol_abs=4e-3, tol_rel=3e-4)
+        assert np.abs(ys[0] - ys[1]).max() <= 4e-3
+
+
 # ---------------------------------------------------------------------------------------------- full-size shapes
 LLAMA32_3B = dict(hidden=3072, inter=8192, kv=1024, rank=64)
 
