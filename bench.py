@@ -39,6 +39,7 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--unfused", action="store_true", help="one launch per module (wrapper protocol) instead of per group")
     ap.add_argument("--split-k", type=int, default=0)
+    ap.add_argument("--prefill-tokens", type=int, default=2048, help="tokens of the extra prefill (GEMM) measurement; 0 = skip")
     return ap.parse_args()
 
 
@@ -331,12 +332,33 @@ def run_gpu(args, shape):
     h2d = sum(v.numel() * v.element_size() for v in plan["inputs"].values())
     d2h = last.numel() * last.element_size()
 
+    # extra: prefill pass of the same stack through the tensor-core GEMM (reported, not the headline value)
+    prefill = None
+    if args.prefill_tokens > 0:
+        Mp = args.prefill_tokens
+        with torch.cuda.stream(stream):
+            pplan = stack.plan(Mp, corrected=True, fuse_groups=not args.unfused)
+        ms_p, _ = timed(make_step(pplan), max(3, min(10, args.steps)), 3, False)
+        stack.check_status(pplan)
+        fl = stack.algorithmic_flops(Mp, corrected=True)
+        prefill = {"tokens": Mp, "ms": ms_p, "tokens_per_s": Mp / (ms_p * 1e-3), "tflops": fl / (ms_p * 1e-3) / 1e12,
+                   "kernel": "gemm_w4a16_kernel (tcgen05)", "flops_per_pass": fl}
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
     peak, peak_src = measured_peaks()
+    if prefill is not None:
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                mp_ = json.load(f)
+            prefill["frac_of_measured_bf16_burst"] = prefill["tflops"] * world / float(mp_["bf16_tflops"]) / world
+            prefill["frac_of_measured_bf16_sustained"] = prefill["tflops"] / float(mp_["bf16_tflops_sustained"])
+        except Exception:  # noqa: BLE001
+            pass
+        prefill["frac_of_nominal_fp16_dense"] = prefill["tflops"] / 2250.0
     alg = stack.algorithmic_bytes(M, corrected=True)
     alg_plain = stack.algorithmic_bytes(M, corrected=False)
     achieved = alg / (ms_step * 1e-3) / 1e9
@@ -350,13 +372,14 @@ def run_gpu(args, shape):
             "e2e": {"value": M / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms},
             "gpu_launches": plan["n"] * args.steps,
-            "roofline": {"bound": "hbm", "kernel": "gemv_fused_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "roofline": {"bound": "hbm", "kernel": "gemv_stream_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "frac_of_8tbs": achieved / 8000.0, "traffic": None,
                          "peak_source": peak_src, "bytes_per_step": alg,
                          "launches_per_step": plan["n"],
                          "note": "algorithmic bytes of one step / CUDA-event time of one step (launch gaps included)"},
             "correction_overhead": {"time_ratio": ms_step / ms_plain, "plain_ms_per_step": ms_plain,
-                                    "byte_ratio_floor": alg / alg_plain}}
+                                    "byte_ratio_floor": alg / alg_plain},
+            "prefill": prefill}
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = gpu_arm_cpu_baseline(args, shape)
     print(json.dumps(line), flush=True)

@@ -2,12 +2,12 @@
 //
 //   Y[M, OC] = X[M, IC] . dequant(Q)^T  +  alpha * r[M, rank] . L[OC, rank]^T  (+ bias),     r = X . R^T
 //
-// One CTA computes a 256-token x 128-column block of Y as two 128x128 fp32 accumulators in tensor memory.
-// K runs through a 4-stage shared-memory ring in steps of 64:
+// One CTA computes a 256-token x 256-column block of Y as four 128x128 fp32 accumulators in tensor memory (256 x 128
+// with a separate correction accumulator when alpha != 1).  K runs through a shared-memory ring in steps of 64:
 //   warp 0      TMA producer: the two 128x64 activation tiles (128-byte swizzle) and the 128 x 32 B packed
 //               int4 tile of the step; in the correction phase the r tiles and the L tile (fp16, swizzled, no
 //               dequantisation) - the correction is simply more K steps of the same pipeline.
-//   warps 2-5   dequantise: thread i turns row i of the packed tile into 64 fp16 values half_rn((code - zero) *
+//   warps 2-9   dequantise: two threads per row turn the packed tile's row into 64 fp16 values half_rn((code - zero) *
 //               scale) - the same exact-integer unpack + one HMUL2 as the stand-alone dequant kernel, so the
 //               shared-memory tile is bit-identical to the reference's dequantised weight - and stores them as
 //               row i of the K-major, 128-byte-swizzled B tile; afterwards they are the epilogue (TMEM -> registers
@@ -34,13 +34,19 @@ constexpr int BM = 128;   // tokens per accumulator (MMA M)
 constexpr int MT = 2;     // accumulators per CTA
 constexpr int BN = 128;   // output columns per CTA (MMA N)
 constexpr int BK = 64;    // K per stage: 128 bytes of fp16 = one swizzle row
-constexpr int kStagesG = 4;
 constexpr int kABytes = BM * BK * 2;        // 16 KB
-constexpr int kBBytes = BN * BK * 2;        // 16 KB
-constexpr int kPBytes = BN * (BK / 8) * 4;  // 4 KB packed
-constexpr int kStageG = MT * kABytes + kBBytes + kPBytes;  // 53248
-constexpr int kGemmThreads = 192;
-constexpr int kGemmSmem = 2048 + kStagesG * kStageG;  // 1 KB of alignment slack + 1 KB of barriers + the ring
+constexpr int kBBytes = BN * BK * 2;        // 16 KB per 128 output columns
+constexpr int kPBytes = BN * (BK / 8) * 4;  // 4 KB packed per 128 output columns
+// NN = 128-column B tiles per CTA.  NN = 2 halves the activation traffic from L2 per flop (the x tile is read once
+// per 256 output columns) and needs all 512 TMEM columns for its four accumulators, so the correction must
+// accumulate in place (alpha == 1); NN = 1 keeps a separate correction accumulator for any alpha.
+template <int NN> struct Cfg {
+  static constexpr int kStages = NN == 2 ? 3 : 4;
+  static constexpr int kStage = MT * kABytes + NN * (kBBytes + kPBytes);
+  static constexpr int kSmem = 2048 + kStages * kStage;  // 1 KB alignment slack + 1 KB of barriers + the ring
+};
+constexpr int kDequantWarps = 8;  // two threads per B-tile row: a single warp per scheduler is latency-bound
+constexpr int kGemmThreads = 64 + 32 * kDequantWarps;
 constexpr uint32_t kGemmSpin = 1u << 18;
 constexpr uint32_t kTmemCols = 512;
 // instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = 128, M = 128
@@ -53,6 +59,7 @@ struct GemmParams {
   void* out;
   uint32_t* status;
   int M, OC, nk1, nk2, w4, sstride, zstride, out_stride, out_fp32, lr_separate, out_vec_ok;
+  int mt;  // 128-token accumulators per CTA actually used (1 or 2): 1 spreads a narrow product over more CTAs
   float alpha;
 };
 struct alignas(64) GemmMaps {
@@ -118,8 +125,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr));
 }
 
+template <int NN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ GemmMaps tm) {
+  constexpr int kStagesG = Cfg<NN>::kStages;
+  constexpr int kStageG = Cfg<NN>::kStage;
+  constexpr int kBOff = MT * kABytes;                 // B tiles inside a stage
+  constexpr int kPOff = MT * kABytes + NN * kBBytes;  // packed tiles inside a stage
   extern __shared__ unsigned char smem[];
   __shared__ int s_abort;
   __shared__ uint32_t s_tmem_base;
@@ -128,8 +140,9 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   const uint32_t full_b = smem0, empty_b = smem0 + 64, bready_b = smem0 + 128, accum_b = smem0 + 192;
   const uint32_t ring = smem0 + 1024;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * (BM * MT);
-  const int n_mt = (m0 + BM < p.M) ? 2 : 1;
+  const int n0 = blockIdx.x * (BN * NN), m0 = blockIdx.y * (BM * p.mt);
+  const int n_mt = (p.mt == 2 && m0 + BM < p.M) ? 2 : 1;
+  const int n_nt = (NN == 2 && n0 + BN < p.OC) ? 2 : 1;
   const int nk = p.nk1 + p.nk2;
 
   if (threadIdx.x == 0) {
@@ -137,7 +150,7 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     for (int i = 0; i < kStagesG; ++i) {
       g_mbar_init(full_b + 8 * i, 1);
       g_mbar_init(empty_b + 8 * i, 1);
-      g_mbar_init(bready_b + 8 * i, 4);
+      g_mbar_init(bready_b + 8 * i, kDequantWarps);
     }
     g_mbar_init(accum_b, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -165,14 +178,14 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         const bool phase1 = it < p.nk1;
         const int kk = phase1 ? it : it - p.nk1;
         const bool packed = phase1 && p.w4;
-        g_mbar_expect_tx(bar, n_mt * kABytes + (packed ? kPBytes : kBBytes));
+        g_mbar_expect_tx(bar, n_mt * kABytes + NN * (packed ? kPBytes : kBBytes));
         const CUtensorMap* ta = phase1 ? &tm.a1 : &tm.a2;
         g_tma_2d(sbase, ta, kk * BK, m0, bar);
         if (n_mt == 2) g_tma_2d(sbase + kABytes, ta, kk * BK, m0 + BM, bar);
-        if (packed)
-          g_tma_2d(sbase + MT * kABytes + kBBytes, &tm.b1, kk * (BK / 8), n0, bar);
-        else
-          g_tma_2d(sbase + MT * kABytes, phase1 ? &tm.b1 : &tm.b2, kk * BK, n0, bar);
+        if (packed)  // one box of 128 NN rows x 32 B
+          g_tma_2d(sbase + kPOff, &tm.b1, kk * (BK / 8), n0, bar);
+        else  // one box of 128 NN rows x 128 B, swizzled: NN consecutive 16 KB operand tiles
+          g_tma_2d(sbase + kBOff, phase1 ? &tm.b1 : &tm.b2, kk * BK, n0, bar);
       }
       ++issued;
       if (++st == kStagesG) {
@@ -206,13 +219,17 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           const uint32_t lr_off = (phase2 && p.lr_separate) ? BN : 0;
           const bool first = phase2 ? (p.lr_separate && it == p.nk1) : (it == 0);
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            if (mt < n_mt) {
+          for (int nn = 0; nn < NN; ++nn) {
 #pragma unroll
-              for (int k16 = 0; k16 < BK / 16; ++k16) {
-                const uint64_t ad = smem_desc_sw128(sbase + mt * kABytes + k16 * 32);
-                const uint64_t bd = smem_desc_sw128(sbase + MT * kABytes + k16 * 32);
-                umma_f16(tmem_base + mt * (2 * BN) + lr_off, ad, bd, (first && k16 == 0) ? 0u : 1u);
+            for (int mt = 0; mt < MT; ++mt) {
+              if (mt < n_mt && nn < n_nt) {
+                const uint32_t acc_col = (NN == 1) ? mt * (2 * BN) + lr_off : (nn * MT + mt) * BN;
+#pragma unroll
+                for (int k16 = 0; k16 < BK / 16; ++k16) {
+                  const uint64_t ad = smem_desc_sw128(sbase + mt * kABytes + k16 * 32);
+                  const uint64_t bd = smem_desc_sw128(sbase + kBOff + nn * kBBytes + k16 * 32);
+                  umma_f16(tmem_base + acc_col, ad, bd, (first && k16 == 0) ? 0u : 1u);
+                }
               }
             }
           }
@@ -229,56 +246,73 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     __syncwarp();
   } else {
     // ================================================================ dequant warps, then epilogue
-    const int rloc = threadIdx.x - 64;  // row of the B tile
-    const int row = n0 + rloc;
-    const bool rvalid = row < p.OC;
-    const uint32_t b_row = (static_cast<uint32_t>(rloc) >> 3) * 1024 + (static_cast<uint32_t>(rloc) & 7) * 128;
-    const uint32_t sw = static_cast<uint32_t>(rloc) & 7;
+    // 256 threads share the 128 NN rows of the step's packed tile: NN half-rows (32 columns) per thread
+    const int dt = threadIdx.x - 64;
+    int rloc[NN], half[NN];
+    bool rvalid[NN];
+    uint32_t b_row[NN], sw[NN];
+#pragma unroll
+    for (int h = 0; h < NN; ++h) {
+      const int item = dt + 256 * h;
+      rloc[h] = item >> 1;
+      half[h] = item & 1;
+      rvalid[h] = (n0 + rloc[h]) < p.OC;
+      b_row[h] = (static_cast<uint32_t>(rloc[h]) >> 3) * 1024 + (static_cast<uint32_t>(rloc[h]) & 7) * 128;
+      sw[h] = static_cast<uint32_t>(rloc[h]) & 7;
+    }
     uint32_t st = 0, ph = 0;
     bool ok = true;
-    // scale / zero-point of this row: group G is needed at steps 2G and 2G+1; the next group's pair is fetched one
+    // scale / zero-point of a row: group G is needed at steps 2G and 2G+1; the next group's pair is fetched one
     // group ahead so that the global-load latency never sits between a stage becoming free and its tile being written
     const int n_groups = (p.nk1 + 1) >> 1;
-    auto fetch_sz = [&](int G, uint32_t& sbits, uint32_t& z) {
+    auto fetch_sz = [&](int h, int G, uint32_t& sbits, uint32_t& z) {
       sbits = 0;
       z = 0;
-      if (rvalid && G < n_groups && p.w4) {
-        sbits = __half_as_ushort(p.scales[static_cast<size_t>(row) * p.sstride + G]);
-        z = nibble(p.qzeros + static_cast<size_t>(row) * p.zstride, G);
+      if (rvalid[h] && G < n_groups && p.w4) {
+        const size_t row = static_cast<size_t>(n0 + rloc[h]);
+        sbits = __half_as_ushort(p.scales[row * p.sstride + G]);
+        z = nibble(p.qzeros + row * p.zstride, G);
       }
     };
-    uint32_t nx_s, nx_z;
-    fetch_sz(0, nx_s, nx_z);
-    uint32_t s2 = 0, zlo = 0, zhi = 0;
+    uint32_t nx_s[NN], nx_z[NN], s2[NN], zlo[NN], zhi[NN];
+#pragma unroll
+    for (int h = 0; h < NN; ++h) {
+      fetch_sz(h, 0, nx_s[h], nx_z[h]);
+      s2[h] = zlo[h] = zhi[h] = 0;
+    }
     for (int it = 0; it < nk; ++it) {
       ok = ok && g_mbar_wait(empty_b + 8 * st, ph ^ 1, abort_flag, p.status);
       if (it < p.nk1 && p.w4) {
         if ((it & 1) == 0) {  // first step of group it/2
-          s2 = nx_s * 0x00010001u;
-          zero_consts(nx_z, zlo, zhi);
-          fetch_sz((it >> 1) + 1, nx_s, nx_z);
+#pragma unroll
+          for (int h = 0; h < NN; ++h) {
+            s2[h] = nx_s[h] * 0x00010001u;
+            zero_consts(nx_z[h], zlo[h], zhi[h]);
+            fetch_sz(h, (it >> 1) + 1, nx_s[h], nx_z[h]);
+          }
         }
         ok = ok && g_mbar_wait(full_b + 8 * st, ph, abort_flag, p.status);
         if (ok) {
           const uint32_t sbase = ring + st * kStageG;
-          const uint32_t pbase = sbase + MT * kABytes + kBBytes + rloc * 32;
-          uint32_t w[8];
-          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(pbase));
-          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                       : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
-                       : "r"(pbase + 16));
-          const uint32_t bbase = sbase + MT * kABytes + b_row;
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {  // 16-byte chunk c = columns 8c .. 8c+7 of the step
-            uint32_t h[4];
-            unpack8_minus_zero(w[c], zlo, zhi, h);
+          for (int h = 0; h < NN; ++h) {
+            const uint32_t pbase = sbase + kPOff + rloc[h] * 32 + half[h] * 16;
+            uint32_t w[4];
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(pbase));
+            const uint32_t bbase = sbase + kBOff + b_row[h];  // row rloc of the NN stacked 128-row tiles
 #pragma unroll
-            for (int i = 0; i < 4; ++i) h[i] = hmul2(h[i], s2);  // (n0,n4) (n1,n5) (n2,n6) (n3,n7), rounded once
-            const uint32_t v0 = prmt(h[0], h[1], 0x5410), v1 = prmt(h[2], h[3], 0x5410);
-            const uint32_t v2 = prmt(h[0], h[1], 0x7632), v3 = prmt(h[2], h[3], 0x7632);
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bbase + ((static_cast<uint32_t>(c) ^ sw) << 4)), "r"(v0),
-                         "r"(v1), "r"(v2), "r"(v3)
-                         : "memory");
+            for (int j = 0; j < 4; ++j) {  // 16-byte chunk c = columns 8c .. 8c+7 of the step
+              const uint32_t c = static_cast<uint32_t>(half[h] * 4 + j);
+              uint32_t hh[4];
+              unpack8_minus_zero(w[j], zlo[h], zhi[h], hh);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) hh[i] = hmul2(hh[i], s2[h]);  // (n0,n4) (n1,n5) (n2,n6) (n3,n7), rounded once
+              const uint32_t v0 = prmt(hh[0], hh[1], 0x5410), v1 = prmt(hh[2], hh[3], 0x5410);
+              const uint32_t v2 = prmt(hh[0], hh[1], 0x7632), v3 = prmt(hh[2], hh[3], 0x7632);
+              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(bbase + ((c ^ sw[h]) << 4)), "r"(v0), "r"(v1),
+                           "r"(v2), "r"(v3)
+                           : "memory");
+            }
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the MMA
         }
@@ -294,22 +328,26 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     // ---- epilogue: this warp owns TMEM lanes 32 (warp % 4) .. +31 = 32 tokens; one token per lane
     ok = ok && g_mbar_wait(accum_b, 0, abort_flag, p.status);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const int q = warp & 3;
-    for (int mt = 0; mt < n_mt; ++mt) {
+    const int q = warp & 3;                          // TMEM lane quadrant this warp may read
+    const int cb0 = ((warp - 2) >> 2) * (BN / 64);   // warps 2-5 take columns 0..63 of a tile, warps 6-9 columns 64..127
+    for (int at = 0; at < NN * MT; ++at) {
+      const int nn = at / MT, mt = at - nn * MT;
+      if (mt >= n_mt || nn >= n_nt) continue;
       const int tok = m0 + mt * BM + q * 32 + lane;
-      for (int cb = 0; cb < BN / 32; ++cb) {
+      const uint32_t acc_col = (NN == 1) ? mt * (2 * BN) : (nn * MT + mt) * BN;
+      for (int cb = cb0; cb < cb0 + BN / 64; ++cb) {
         uint32_t acc[32], lr[32];
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + mt * (2 * BN) + cb * 32;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc_col + cb * 32;
         tmem_ld32(taddr, acc);
-        if (p.lr_separate) tmem_ld32(taddr + BN, lr);
+        if (NN == 1 && p.lr_separate) tmem_ld32(taddr + BN, lr);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const int c0 = n0 + cb * 32;
+        const int c0 = n0 + nn * BN + cb * 32;
         if (ok && tok < p.M) {
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             v[j] = __uint_as_float(acc[j]);
-            if (p.lr_separate) v[j] = fmaf(p.alpha, __uint_as_float(lr[j]), v[j]);
+            if (NN == 1 && p.lr_separate) v[j] = fmaf(p.alpha, __uint_as_float(lr[j]), v[j]);
             if (p.bias && c0 + j < p.OC) v[j] += __half2float(p.bias[c0 + j]);
           }
           if (p.out_fp32) {
@@ -359,18 +397,24 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
 inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int cdiv(int a, int b) { return (a + b - 1) / b; }
 
-cudaError_t launch_gemm(const GemmParams& p, const GemmMaps& tm, cudaStream_t stream) {
+template <int NN>
+cudaError_t launch_gemm_nn(const GemmParams& p, const GemmMaps& tm, cudaStream_t stream) {
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_kernel<NN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NN>::kSmem);
     if (e != cudaSuccess) return e;
     attr_done[dev] = true;
   }
-  dim3 grid(cdiv(p.OC, BN), cdiv(p.M, BM * MT));
-  gemm_w4a16_kernel<<<grid, kGemmThreads, kGemmSmem, stream>>>(p, tm);
+  dim3 grid(cdiv(p.OC, BN * NN), cdiv(p.M, BM * p.mt));
+  gemm_w4a16_kernel<NN><<<grid, kGemmThreads, Cfg<NN>::kSmem, stream>>>(p, tm);
   return cudaGetLastError();
+}
+
+// nn = 2 needs in-place accumulation of the correction (no separate accumulator columns left).
+cudaError_t launch_gemm(const GemmParams& p, const GemmMaps& tm, int nn, cudaStream_t stream) {
+  return nn == 2 ? launch_gemm_nn<2>(p, tm, stream) : launch_gemm_nn<1>(p, tm, stream);
 }
 
 }  // namespace
@@ -414,7 +458,10 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
     GemmMaps tm;
     std::memset(&tm, 0, sizeof(tm));
     tm.a1 = tm_x;
-    if ((rc = map(&tm.b1, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.R, g.IC, g.rank, static_cast<uint64_t>(g.R_stride) * 2, BK, BN, 1)))
+    const int nn = 1;  // narrow output (rank columns): small tiles, more CTAs
+    p.mt = 1;
+    if ((rc = map(&tm.b1, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.R, g.IC, g.rank, static_cast<uint64_t>(g.R_stride) * 2, BK, BN * nn,
+                  1)))
       return rc;
     tm.a2 = tm.a1;
     tm.b2 = tm.b1;
@@ -429,7 +476,7 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
     p.out_fp32 = 0;
     p.alpha = 1.f;
     p.out_vec_ok = 1;  // rank % 8 == 0 and r_buf aligned
-    cudaError_t e = launch_gemm(p, tm, stream);
+    cudaError_t e = launch_gemm(p, tm, nn, stream);
     if (e != cudaSuccess) {
       *cuda_err = e;
       return GLOWQ_ERR_CUDA;
@@ -444,17 +491,20 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
   for (int i = 0; i < g.n_members; ++i) {
     const auto& m = g.members[i];
     const bool corr = g.r_mode != GLOWQ_R_NONE && m.L && m.alpha != 0.f;
+    const bool lr_separate = corr && m.alpha != 1.f;
+    const int nn = (!lr_separate && m.OC >= 2 * BN) ? 2 : 1;
     GemmParams p{};
     GemmMaps tm;
     std::memset(&tm, 0, sizeof(tm));
     tm.a1 = tm_x;
     if ((rc = map(&tm.b1, CU_TENSOR_MAP_DATA_TYPE_INT32, m.qweight, static_cast<uint64_t>(G) * 16, m.OC,
-                  static_cast<uint64_t>(m.weight_stride_i32) * 4, BK / 8, BN, 0)))
+                  static_cast<uint64_t>(m.weight_stride_i32) * 4, BK / 8, BN * nn, 0)))
       return rc;
     tm.a2 = corr ? tm_r : tm_x;
     tm.b2 = tm.b1;
     if (corr &&
-        (rc = map(&tm.b2, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, m.L, g.rank, m.OC, static_cast<uint64_t>(m.L_stride) * 2, BK, BN, 1)))
+        (rc = map(&tm.b2, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, m.L, g.rank, m.OC, static_cast<uint64_t>(m.L_stride) * 2, BK, BN * nn,
+                  1)))
       return rc;
     p.scales = static_cast<const __half*>(m.scales);
     p.qzeros = m.qzeros;
@@ -471,10 +521,11 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
     p.out_stride = m.out_stride;
     p.out_fp32 = g.out_dtype == GLOWQ_OUT_F32;
     p.alpha = m.alpha;
-    p.lr_separate = corr && m.alpha != 1.f;
+    p.lr_separate = lr_separate;
+    p.mt = 2;
     const int esz = p.out_fp32 ? 4 : 2;
     p.out_vec_ok = al16(m.out) && ((static_cast<size_t>(m.out_stride) * esz) % 16 == 0);
-    cudaError_t e = launch_gemm(p, tm, stream);
+    cudaError_t e = launch_gemm(p, tm, nn, stream);
     if (e != cudaSuccess) {
       *cuda_err = e;
       return GLOWQ_ERR_CUDA;
