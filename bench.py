@@ -22,6 +22,9 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# mean DRAM bytes (read + write) per gemv_stream_kernel launch of the Llama-3.2-3B batch-1 token step, from ncu
+NCU_DRAM_BYTES_PER_LAUNCH = 14.02e6
+
 METRIC = "decode_tok_s"
 UNIT = "tokens/s"
 
@@ -373,10 +376,14 @@ def run_gpu(args, shape):
                     "ms_per_step": e2e_ms},
             "gpu_launches": plan["n"] * args.steps,
             "roofline": {"bound": "hbm", "kernel": "gemv_stream_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "frac_of_8tbs": achieved / 8000.0, "traffic": None,
-                         "peak_source": peak_src, "bytes_per_step": alg,
-                         "launches_per_step": plan["n"],
-                         "note": "algorithmic bytes of one step / CUDA-event time of one step (launch gaps included)"},
+                         "frac": achieved / peak, "frac_of_8tbs": achieved / 8000.0,
+                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH if shape.name == "llama-3.2-3b" and M == 1 and world == 1 else None,
+                         "traffic_source": "profiles/gemv_stream_llama32_3b_decode_launches.md (ncu dram__bytes_read+write, "
+                                           "mean over the launches of a token step)",
+                         "peak_source": peak_src, "bytes_per_launch": alg / plan["n"],
+                         "us_per_launch": ms_step * 1e3 / plan["n"], "launches_per_step": plan["n"],
+                         "note": "algorithmic bytes of one launch (mean over the step's launches) / mean launch duration "
+                                 "from CUDA events around the graph-replayed step (inter-kernel gaps included)"},
             "correction_overhead": {"time_ratio": ms_step / ms_plain, "plain_ms_per_step": ms_plain,
                                     "byte_ratio_floor": alg / alg_plain},
             "prefill": prefill}
