@@ -39,6 +39,10 @@ def parse_args():
     ap.add_argument("--impl", default="glowq_b200", choices=["glowq_b200", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (debugging only)")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--graph-collectives", action="store_true",
+                    help="with N > 1, capture the NCCL all-reduces into the CUDA graph too (default: graphs per segment, "
+                         "all-reduces launched between them)")
+    ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--unfused", action="store_true", help="one launch per module (wrapper protocol) instead of per group")
     ap.add_argument("--split-k", type=int, default=0)
@@ -218,8 +222,14 @@ def run_gpu(args, shape):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
+    def log(msg):
+        if args.verbose:
+            print(f"[bench rank {rank}] {msg}", file=sys.stderr, flush=True)
+
     M = args.batch
+    log("building the stack")
     stack = LinearStack(shape, dev, seed=0, layers=args.layers, tp_rank=rank, tp_world=world)
+    log("stack built")
     stream = torch.cuda.Stream(dev)
     with torch.cuda.stream(stream):
         plan = stack.plan(M, corrected=True, fuse_groups=not args.unfused, split_k=args.split_k)
@@ -239,13 +249,11 @@ def run_gpu(args, shape):
         return pts
 
     def make_step(p):
+        """(callable that enqueues one step, list of segments).  With one rank a step is one C call; with N ranks it is
+        a list of (group calls, tensor to all-reduce) segments ending at the row-split linears."""
         if world == 1:
-            return lambda: stack.step(p)
+            return (lambda: stack.step(p)), None
         pts = reduce_points(p)
-        outs = []
-        for c in p["calls"]:
-            pass
-        # tensors to reduce live in plan["keep"]: find by pointer
         ptr2t = {}
         for item in p["keep"]:
             if isinstance(item, list):
@@ -262,22 +270,37 @@ def run_gpu(args, shape):
             for arr, n, t in segs:
                 stack.ext.check(stack.ext.lib.glowq_w4a16_group_forward_many(arr, n), "group_forward_many")
                 dist.all_reduce(t)
-        return step
+        return step, segs
 
-    def timed(step_fn, steps, warmup, use_graph):
+    def timed(step_and_segs, steps, warmup, use_graph):
+        step_fn, segs = step_and_segs
         with torch.cuda.stream(stream):
-            graph = None
             for _ in range(max(3, warmup)):
                 step_fn()
             stream.synchronize()
-            if use_graph:
+            run = step_fn
+            if use_graph and (segs is None or args.graph_collectives):
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph, stream=stream):
                     step_fn()
-                for _ in range(3):
-                    graph.replay()
-                stream.synchronize()
-            run = graph.replay if graph is not None else step_fn
+                run = graph.replay
+            elif use_graph:
+                # one graph per segment of group launches; the all-reduces are enqueued between the replays
+                graphs = []
+                for arr, n, t in segs:
+                    g_ = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g_, stream=stream):
+                        stack.ext.check(stack.ext.lib.glowq_w4a16_group_forward_many(arr, n), "group_forward_many")
+                    graphs.append((g_, t))
+
+                def run():
+                    for g_, t in graphs:
+                        g_.replay()
+                        dist.all_reduce(t)
+            for _ in range(3):
+                run()
+            stream.synchronize()
+            log("warm-up done")
             if world > 1:
                 dist.barrier()
             torch.cuda.synchronize()
@@ -295,6 +318,7 @@ def run_gpu(args, shape):
                 t = torch.tensor([ms], device=dev)
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 ms = float(t.item())
+            log(f"timed {steps} steps: {ms / steps:.4f} ms/step")
         return ms / steps, run
 
     use_graph = not args.no_graph

@@ -202,7 +202,7 @@ GemvPlan make_plan(int M, int IC, int n_tiles, int rank, int sms, int split_k) {
   if (forced_stages > 0 && pl.stages > 0) pl.stages = std::max(2, std::min(forced_stages, pl.stages));
   pl.smem = plan_smem(pl, Mc, pl.stages);
   pl.n_r_tiles = ceil_div(std::max(rank, 0), kRTileRows);
-  pl.SKr = std::min(4, chunks);   // consumers add the K slices of r themselves: keep them few
+  pl.SKr = chunks;   // one quantisation group per warp and R unit: a single round of loads per unit
   const size_t tile_elems = static_cast<size_t>(kRowTiles) * pl.NT * 128;
   size_t off = kWsHeaderBytes;
   pl.off_r_ctr = off;
@@ -342,8 +342,10 @@ int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cuda
     if (fast) {
       if (pl.stages < 2 || gemv_smem_bytes(p, pl.NT) > kSmemOnePerSm) return GLOWQ_ERR_UNSUPPORTED_SHAPE;
       // persistent grid: every CTA resident at once, a whole number of CTAs per K slice
-      int grid = std::min(dev.sms * pl.ctas_per_sm, n_tiles * pl.SK);
-      grid = std::max(pl.SK, grid / pl.SK * pl.SK);
+      // few R units: dedicated CTAs at the end of the grid; many (large rank x IC): every CTA runs its share first
+      p.n_r_ctas = p.n_r_units <= 32 ? p.n_r_units : 0;
+      int grid = std::min(dev.sms * pl.ctas_per_sm - p.n_r_ctas, n_tiles * pl.SK);
+      grid = std::max(pl.SK, grid / pl.SK * pl.SK) + p.n_r_ctas;
       p.l_cols = std::min(std::max(p.rank, 8), 256);
       alignas(64) TensorMaps tm;
       std::memset(&tm, 0, sizeof(tm));

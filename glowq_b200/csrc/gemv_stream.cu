@@ -13,12 +13,14 @@
 //     activations staged once per CTA in B-fragment order (tokens on the MMA N axis, so up to 8 tokens cost what
 //     one token costs).  Each group's fp32 result is scaled by its fp16 scale, and the zero-point is applied as
 //     -z * scale * sum(x over the group), in fp32.
-//   * r = R_g . x is produced inside the launch by "R units" (16 rows of R x 1024 columns) that the consumer warps
-//     of the last CTAs run before their first tile; the last unit of an R tile sums the partials in a fixed
-//     order, rounds r to fp16 into r_buf and bumps a release counter.  The grid never exceeds what is resident
-//     at once, so the bounded wait before the first L_i epilogue never depends on an unscheduled CTA.
+//   * r = R_g . x is produced inside the launch by "R units" (16 rows of R x a K slice) run by a few extra CTAs at
+//     the end of the grid; each unit stores an fp32 slot and bumps a release counter, and whoever needs r adds the
+//     slots of an R tile in slot order (identical bits everywhere) and rounds to fp16.  The grid never exceeds what
+//     is resident at once, so the bounded wait before the first L_i epilogue never depends on an unscheduled CTA.
 //   * K can be sliced across CTAs; the last CTA to arrive at a tile sums the slices in slice order.
 // Every wait (mbarrier, release counter) is bounded; on expiry the kernel records a status word and drains.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "params.h"
 
@@ -209,7 +211,7 @@ __device__ __forceinline__ void cross_warp_reduce(float (&acc)[NB][4], float* re
 // fp32 result goes to the unit's own slot of r_partial and the release counter is bumped; whoever needs r adds
 // the SKr slots of an R tile in slot order (so every reader, and r_buf, see the same bits).
 template <int NT>
-__device__ __forceinline__ void r_unit(const GemvParams& p, int unit, float* red, float* fin) {
+__device__ __forceinline__ void r_unit(const GemvParams& p, int unit, float* red, float* fin, bool& dep_wait_pending) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int rt = unit / p.SKr, ks = unit - rt * p.SKr;
   const int j0 = rt * kRTileRows;
@@ -228,6 +230,10 @@ __device__ __forceinline__ void r_unit(const GemvParams& p, int unit, float* red
       const bool ok = (k + 8 <= p.IC);
       a[i] = ok ? ldg_stream_v4(rowA + k) : make_uint4(0, 0, 0, 0);
       b[i] = ok ? ldg_stream_v4(rowB + k) : make_uint4(0, 0, 0, 0);
+    }
+    if (dep_wait_pending) {  // R is static, x is not: the earlier kernels must be complete before x is read
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      dep_wait_pending = false;
     }
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
@@ -251,6 +257,10 @@ __device__ __forceinline__ void r_unit(const GemvParams& p, int unit, float* red
         mma16816(acc[nt], a[i].z, b[i].z, a[i].w, b[i].w, xv.z, xv.w);
       }
     }
+  }
+  if (dep_wait_pending) {  // (a warp without a group of its own in this unit)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    dep_wait_pending = false;
   }
   cross_warp_reduce<NT>(acc, red, fin);  // fin[nt*128 + tok8*16 + row16]
   float* slot = p.r_partial + static_cast<size_t>(unit) * (NT * 128);
@@ -335,14 +345,30 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int S = p.stages;
+  // The last n_r_ctas CTAs of the grid only compute r (their copy / aux warps have no tiles): a CTA that ran an R
+  // unit AND a full share of row tiles would finish microseconds after the others and set the kernel's length.
+  const int n_main = static_cast<int>(gridDim.x) - p.n_r_ctas;
+  const bool r_only = static_cast<int>(blockIdx.x) >= n_main;
   const int slice = blockIdx.x % p.SK;
-  const int first_tile = blockIdx.x / p.SK;
-  const int tile_step = gridDim.x / p.SK;
+  const int first_tile = r_only ? p.n_tiles : static_cast<int>(blockIdx.x) / p.SK;
+  const int tile_step = n_main / p.SK;
+  // k-th row tile of this CTA (>= n_tiles: none left).  With K slices every CTA of a slice strides over the tiles.
+  // Without, the first round of tiles goes to the main CTAs only and the rest is dealt over ALL CTAs, so that the
+  // CTAs that computed r pick up row tiles afterwards instead of idling through a long launch.
+  const bool deal_all = (p.SK == 1 && p.n_r_ctas > 0);
+  auto tile_at = [&](int k) -> int {
+    if (!deal_all) return first_tile + k * tile_step;
+    if (r_only) return n_main + static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
+    return k == 0 ? static_cast<int>(blockIdx.x) : n_main + static_cast<int>(blockIdx.x) + (k - 1) * static_cast<int>(gridDim.x);
+  };
   const int g0 = slice * p.gps;
   const int ng = min(p.G, g0 + p.gps) - g0;
   const int n_chunks = (ng + kChunkGroups - 1) / kChunkGroups;
   const int n_lstages = (p.rank + 255) >> 8;
 
+  // Programmatic dependent launch: let the next kernel of the stream start its own prologue (barrier set-up, weight
+  // and metadata copies - nothing that depends on this kernel) as soon as every CTA of this grid is resident.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == 0) {
     s_abort = 0;
     for (int i = 0; i < kMaxStages; ++i) {
@@ -369,7 +395,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     // bulk copies of 512 B cap the copy engine at a fraction of HBM rate; one 16 KB box per instruction does not.
     uint32_t st = 0, ph = 0, issued = 0;
     bool ok = true;
-    for (int tile = first_tile; tile < p.n_tiles && ok; tile += tile_step) {
+    for (int k = 0, tile; (tile = tile_at(k)) < p.n_tiles && ok; ++k) {
       const TileInfo ti = tile_info(p, tile, slice);
       for (int c = 0; c < n_chunks; ++c) {
         if (!(ok = mbar_wait_u32(empty_u32 + st * 8, ph ^ 1, cx))) break;
@@ -420,10 +446,11 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     // combine, bias and the store, and hands the buffer back.  Consumers therefore never wait for one another.
     uint32_t slot = 0, ph = 0, buf = 0;
     int issued = 0, done = 0;
-    int tile_m = first_tile;
+    int k_m = 0;
     bool ok = true;
-    for (int tile = first_tile; tile < p.n_tiles; tile += tile_step) {
-      while (ok && tile_m < p.n_tiles && issued - done < kMetaDepth) {
+    for (int k = 0, tile; (tile = tile_at(k)) < p.n_tiles; ++k) {
+      while (ok && tile_at(k_m) < p.n_tiles && issued - done < kMetaDepth) {
+        const int tile_m = tile_at(k_m);
         const TileInfo tm_i = tile_info(p, tile_m, slice);
         const MemberDev& mbm = p.mem[tm_i.mi];
         if (!(ok = mbar_wait_u32(mempty_u32 + slot * 8, ph ^ 1, cx))) break;
@@ -448,10 +475,11 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
           ph ^= 1;
         }
         ++issued;
-        tile_m += tile_step;
+        ++k_m;
       }
 
-      // ---- epilogue of `tile`
+      // ---- epilogue of `tile` (outputs may still be read by the previous kernel until it has completed)
+      if (k == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
       const TileInfo ti = tile_info(p, tile, slice);
       const MemberDev& mb = p.mem[ti.mi];
       if (buf == 0)
@@ -533,14 +561,21 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   } else {
     // ================================================================ consumer warps
     const int g = lane >> 2, t = lane & 3;
-    stage_x(p, g0, ng, xs, xsum, 8 * NT);
-    consumer_sync();  // publishes xs / xsum
-    if (p.r_mode == 1) {
-      // R units are dealt from the last CTA downwards (those CTAs hold the fewest row tiles).  The grid is
-      // persistent - never larger than what is resident at once - so every unit's owner is running.
+    bool dep_wait_pending = true;  // x (and a loaded r) come from earlier kernels of the stream
+    if (r_only) {
+      // The grid is persistent - never larger than what is resident at once - so every unit's owner is running
+      // while the other CTAs wait (bounded) for r before their first L epilogue.  R loads go out before the
+      // dependency wait; x is staged only afterwards, for the row tiles this CTA picks up later.
+      for (int u = static_cast<int>(blockIdx.x) - n_main; u < p.n_r_units; u += p.n_r_ctas)
+        r_unit<NT>(p, u, red, fin, dep_wait_pending);
+    } else if (p.r_mode == 1 && p.n_r_ctas == 0) {
+      // a large right factor: every CTA takes its share of R units (dealt from the last CTA down) before its tiles
       for (int u = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x); u < p.n_r_units; u += gridDim.x)
-        r_unit<NT>(p, u, red, fin);
+        r_unit<NT>(p, u, red, fin, dep_wait_pending);
     }
+    if (dep_wait_pending) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (!r_only || deal_all) stage_x(p, g0, ng, xs, xsum, 8 * NT);
+    consumer_sync();  // publishes xs / xsum
 
     // per-lane constant shared addresses: weight quad (warp's group, lane's 16 B, lane's row), x chunk, x sums
     const uint32_t ring_lane = smem_u32(ring) + warp * 64 + t * 16 + g * kRowPitch;
@@ -554,8 +589,9 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     for (int nt = 0; nt < NT; ++nt) tokv[nt] = (nt * 8 + g) < p.M;
 
     uint32_t st = 0, ph = 0, slot = 0, mph = 0, rbuf = 0, rph = 0;
-    bool ok = true, r_ready = (p.r_mode != 1);
-    for (int tile = first_tile; tile < p.n_tiles; tile += tile_step) {
+    bool ok = true, r_ready = (p.r_mode != 1), rb_cached = false;
+    uint4 rb_keep[NT];  // r fragments of this lane (first L stage): the same for every row tile of the CTA
+    for (int k = 0, tile; (tile = tile_at(k)) < p.n_tiles; ++k) {
       const TileInfo ti = tile_info(p, tile, slice);
       const MemberDev& mb = p.mem[ti.mi];
       ok = ok && mbar_wait_u32(mfull_u32 + slot * 8, mph, cx);
@@ -651,11 +687,21 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
             const uint32_t lpitch = static_cast<uint32_t>(p.l_cols) * 2u;  // dense rows of the L box
             const uint32_t lbase = smem_u32(ring) + st * kStageBytes + g * lpitch + k * 2;
             uint4 rb[NT];
+            if (l == 0 && rb_cached) {
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-              rb[nt] = !(kin && tokv[nt]) ? make_uint4(0, 0, 0, 0)
-                       : (p.r_mode == 1)     ? r_frag_from_partials<NT>(p, nt * 8 + g, 256 * l + k)
-                                             : ldg_cg_v4(p.r_buf + static_cast<size_t>(nt * 8 + g) * p.rank + 256 * l + k);
+              for (int nt = 0; nt < NT; ++nt) rb[nt] = rb_keep[nt];
+            } else {
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt)
+                rb[nt] = !(kin && tokv[nt]) ? make_uint4(0, 0, 0, 0)
+                         : (p.r_mode == 1)     ? r_frag_from_partials<NT>(p, nt * 8 + g, 256 * l + k)
+                                               : ldg_cg_v4(p.r_buf + static_cast<size_t>(nt * 8 + g) * p.rank + 256 * l + k);
+              if (l == 0) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) rb_keep[nt] = rb[nt];
+                rb_cached = true;
+              }
+            }
 #pragma unroll
             for (int j = 0; j < RT; ++j) {
               const uint4 la = kin ? lds128(lbase + (j * 16) * lpitch) : make_uint4(0, 0, 0, 0);
@@ -808,8 +854,21 @@ static cudaError_t launch_nt(const GemvParams& p, const TensorMaps& tm, int grid
     if (e != cudaSuccess) return e;
     attr_done[dev] = true;
   }
-  gemv_stream_kernel<NT><<<grid, kGemvThreads, gemv_smem_bytes(p, NT), stream>>>(p, tm);
-  return cudaGetLastError();
+  static const bool use_pdl = [] {
+    const char* v = std::getenv("GLOWQ_PDL");
+    return !(v && v[0] == '0');
+  }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kGemvThreads);
+  cfg.dynamicSmemBytes = gemv_smem_bytes(p, NT);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT>, p, tm);
 }
 
 cudaError_t launch_gemv_stream(const GemvParams& p, const TensorMaps& tm, int NT, int grid, cudaStream_t stream) {
