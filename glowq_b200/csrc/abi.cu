@@ -175,8 +175,11 @@ GemvPlan make_plan(int M, int IC, int n_tiles, int rank, int sms, int split_k) {
   int sk = 1;
   if (split_k > 0) {
     sk = std::min(split_k, chunks);
-  } else if (n_tiles < sms) {  // too few row tiles to give every SM one: slice K as well
-    sk = std::min(ceil_div(sms, std::max(1, n_tiles)), chunks);
+  } else if (n_tiles < 2 * sms && chunks >= 8) {
+    // Fewer row tiles than resident CTAs AND long rows: slice K too.  Measured on B200: the split-K combine (fence,
+    // counter, re-read of the partial tiles) costs a few microseconds per tile, so it only pays when a CTA would
+    // otherwise stream >= 8 stages alone (down_proj shapes); short rows (o_proj, k/v) are faster unsliced.
+    sk = std::max(1, std::min(ceil_div(2 * sms, std::max(1, n_tiles)), chunks / 4));
   }
   for (;; ++sk) {
     pl.gps = ceil_div(chunks, sk) * kChunkGroups;   // whole pipeline stages per slice
