@@ -492,7 +492,26 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
     const auto& m = g.members[i];
     const bool corr = g.r_mode != GLOWQ_R_NONE && m.L && m.alpha != 0.f;
     const bool lr_separate = corr && m.alpha != 1.f;
-    const int nn = (!lr_separate && m.OC >= 2 * BN) ? 2 : 1;
+    // Tile shape per launch: the 256 x 256 CTA tile has the best operand reuse, but a problem that fills the SMs
+    // badly in whole waves is faster with narrower (nn = 1) or shorter (mt = 1) tiles.
+    int nn = 1, mt = 2;
+    {
+      int sms = 148;
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+      double best = -1.0;
+      const int nn_max = (!lr_separate && m.OC >= 2 * BN) ? 2 : 1;
+      for (int cnn = nn_max; cnn >= 1; --cnn)
+        for (int cmt = 2; cmt >= 1; --cmt) {
+          const long tiles = static_cast<long>(cdiv(m.OC, BN * cnn)) * cdiv(g.M, BM * cmt);
+          const double wave_eff = static_cast<double>(tiles) / (static_cast<double>(cdiv(static_cast<int>(tiles), sms)) * sms);
+          const double reuse = (cnn == 2 ? 1.0 : 0.85) * (cmt == 2 ? 1.0 : 0.88);
+          if (wave_eff * reuse > best) {
+            best = wave_eff * reuse;
+            nn = cnn;
+            mt = cmt;
+          }
+        }
+    }
     GemmParams p{};
     GemmMaps tm;
     std::memset(&tm, 0, sizeof(tm));
@@ -522,7 +541,7 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
     p.out_fp32 = g.out_dtype == GLOWQ_OUT_F32;
     p.alpha = m.alpha;
     p.lr_separate = lr_separate;
-    p.mt = 2;
+    p.mt = mt;
     const int esz = p.out_fp32 ? 4 : 2;
     p.out_vec_ok = al16(m.out) && ((static_cast<size_t>(m.out_stride) * esz) % 16 == 0);
     cudaError_t e = launch_gemm(p, tm, nn, stream);
