@@ -139,7 +139,8 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-constexpr int kGemvMaxM = 32;                 // tokens per launch of the weight-streaming kernel
+constexpr int kGemvMaxM = 8;                  // tokens per launch of the weight-streaming kernel (one MMA N tile)
+constexpr int kGemvAutoMaxM = 16;             // GLOWQ_KERNEL_AUTO: up to two such launches, the tensor-core GEMM above
 constexpr size_t kSmemTwoPerSm = 112 * 1024;  // dynamic shared memory that still lets two CTAs share an SM
 constexpr size_t kSmemOnePerSm = 224 * 1024;
 
@@ -439,7 +440,16 @@ int glowq_w4a16_group_forward(const glowq_w4a16_group_t* group) {
   if (rc != GLOWQ_OK) return rc;
   if (g.M == 0) return GLOWQ_OK;
   cudaStream_t stream = static_cast<cudaStream_t>(g.stream);
-  bool use_gemm = g.kernel == GLOWQ_KERNEL_GEMM || (g.kernel == GLOWQ_KERNEL_AUTO && g.M > kGemvMaxM);
+  // Measured on B200: 8 tokens stream at the cost of one, so M tokens cost ceil(M/8) streaming launches.  The tcgen05
+  // GEMM takes about the same time for anything up to 256 tokens (it is bound by dequantising the weight once), which
+  // beats 3-4 streaming launches only for large weights (Qwen3-14B gate/up: 145 us vs 180 us at M = 32; Llama-3.2-3B
+  // q/k/v: 122 us vs 52 us).  Above 32 tokens the GEMM wins everywhere.
+  bool use_gemm = g.kernel == GLOWQ_KERNEL_GEMM;
+  if (g.kernel == GLOWQ_KERNEL_AUTO) {
+    double weights = 0;
+    for (int i = 0; i < g.n_members; ++i) weights += static_cast<double>(g.members[i].OC) * g.IC;
+    use_gemm = g.M > 32 || (g.M > kGemvAutoMaxM && weights >= 1.0e8);
+  }
   if (use_gemm && gemm_supported(g)) {
     cudaError_t ce = cudaSuccess;
     rc = gemm_group_forward(g, stream, &ce);

@@ -131,7 +131,7 @@ class CudaW4A16Linear(nn.Module):
 
     def kernel_choice(self, m: int) -> int:
         """Which kernel a call with ``m`` tokens asks for.  The library's own switch-over (weight-streaming
-        kernel up to 32 tokens, tensor-core kernel above) applies unless a FORCE knob is set."""
+        kernel up to 16 tokens, tensor-core kernel above) applies unless a FORCE knob is set."""
         if self._force_gemm:
             return K.KERNEL_GEMM
         if self._force_gemv:
