@@ -46,6 +46,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--unfused", action="store_true", help="one launch per module (wrapper protocol) instead of per group")
     ap.add_argument("--split-k", type=int, default=0)
+    ap.add_argument("--glowq-s-fraction", type=float, default=1.0,
+                    help="GlowQ-S: fraction of the (layer, group) pairs that keep their correction (seed 3); the rest run "
+                         "plain W4A16")
     ap.add_argument("--prefill-tokens", type=int, default=2048, help="tokens of the extra prefill (GEMM) measurement; 0 = skip")
     return ap.parse_args()
 
@@ -54,7 +57,7 @@ def workload_config(args, shape, extra=None):
     cfg = {"workload": f"{shape.name}-shaped stack, {args.layers or shape.layers} layers x 7 corrected W4A16 linears "
                        f"(g128, rank {shape.rank}), decode token step, batch {args.batch}",
            "scope": "linears only (the hot path); attention, norms, embedding and lm_head are not in the step",
-           "batch": args.batch, "rank": shape.rank, "group_size": 128,
+           "batch": args.batch, "rank": shape.rank, "group_size": 128, "glowq_s_fraction": args.glowq_s_fraction,
            "l2_policy": "weights per step exceed L2 (inputs larger than L2)"}
     if extra:
         cfg.update(extra)
@@ -228,7 +231,18 @@ def run_gpu(args, shape):
 
     M = args.batch
     log("building the stack")
-    stack = LinearStack(shape, dev, seed=0, layers=args.layers, tp_rank=rank, tp_world=world)
+    enabled = None
+    n_layers_cfg = args.layers or shape.layers
+    if args.glowq_s_fraction < 1.0:
+        # seeded subset of the 4 x layers (layer, group) pairs, as the selective-restoration sweep would enable them
+        keys = []
+        for li in range(n_layers_cfg):
+            keys += [f"layer{li}_qkv", f"model.layers.{li}.self_attn.o_proj", f"layer{li}_mlp",
+                     f"model.layers.{li}.mlp.down_proj"]
+        gsel = torch.Generator().manual_seed(3)
+        perm = torch.randperm(len(keys), generator=gsel)[:int(round(args.glowq_s_fraction * len(keys)))]
+        enabled = {keys[i] for i in perm.tolist()}
+    stack = LinearStack(shape, dev, seed=0, layers=args.layers, tp_rank=rank, tp_world=world, enabled_groups=enabled)
     log("stack built")
     stream = torch.cuda.Stream(dev)
     with torch.cuda.stream(stream):
