@@ -17,6 +17,7 @@
 // The dequantised weight never goes to HBM (the reference writes and re-reads a full fp16 copy per call).
 // The same kernel with an fp16 B operand by TMA (no dequant warps' work) computes r = X . R^T.
 // Every mbarrier wait is bounded; on expiry a status word is set and the CTA drains and frees its tensor memory.
+#include <algorithm>
 #include <cstring>
 
 #include "../../include/glowq_w4a16.h"
@@ -52,18 +53,23 @@ constexpr uint32_t kTmemCols = 512;
 // instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = 128, M = 128
 constexpr uint32_t kIdesc = (1u << 4) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
 
-struct GemmParams {
+struct GemmMember {   // one linear of the group; its column tiles are blockIdx.x in [tile_begin, next tile_begin)
   const __half* scales;
   const int32_t* qzeros;
   const __half* bias;
   void* out;
-  uint32_t* status;
-  int M, OC, nk1, nk2, w4, sstride, zstride, out_stride, out_fp32, lr_separate, out_vec_ok;
-  int mt;  // 128-token accumulators per CTA actually used (1 or 2): 1 spreads a narrow product over more CTAs
+  int OC, nk2, sstride, zstride, out_stride, lr_separate, out_vec_ok, tile_begin;
   float alpha;
 };
+struct GemmParams {
+  uint32_t* status;
+  int M, nk1, w4, out_fp32, n_members;
+  int mt;  // 128-token accumulators per CTA actually used (1 or 2): 1 spreads a narrow product over more CTAs
+  GemmMember mem[kMaxMembers];
+};
 struct alignas(64) GemmMaps {
-  CUtensorMap a1, b1, a2, b2;  // phase 1: x, packed weight (or fp16 B); phase 2: r, L
+  CUtensorMap a1, a2;                          // activations: x (phase 1), r (phase 2)
+  CUtensorMap b1[kMaxMembers], b2[kMaxMembers];  // per member: packed weight (or fp16 B), L
 };
 
 __device__ __forceinline__ uint32_t sm_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -140,10 +146,15 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   const uint32_t full_b = smem0, empty_b = smem0 + 64, bready_b = smem0 + 128, accum_b = smem0 + 192;
   const uint32_t ring = smem0 + 1024;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * (BN * NN), m0 = blockIdx.y * (BM * p.mt);
+  int mi = 0;
+#pragma unroll
+  for (int i = 1; i < kMaxMembers; ++i)
+    if (i < p.n_members && static_cast<int>(blockIdx.x) >= p.mem[i].tile_begin) mi = i;
+  const GemmMember& mb = p.mem[mi];
+  const int n0 = (static_cast<int>(blockIdx.x) - mb.tile_begin) * (BN * NN), m0 = blockIdx.y * (BM * p.mt);
   const int n_mt = (p.mt == 2 && m0 + BM < p.M) ? 2 : 1;
-  const int n_nt = (NN == 2 && n0 + BN < p.OC) ? 2 : 1;
-  const int nk = p.nk1 + p.nk2;
+  const int n_nt = (NN == 2 && n0 + BN < mb.OC) ? 2 : 1;
+  const int nk = p.nk1 + mb.nk2;
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -183,9 +194,9 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         g_tma_2d(sbase, ta, kk * BK, m0, bar);
         if (n_mt == 2) g_tma_2d(sbase + kABytes, ta, kk * BK, m0 + BM, bar);
         if (packed)  // one box of 128 NN rows x 32 B
-          g_tma_2d(sbase + kPOff, &tm.b1, kk * (BK / 8), n0, bar);
+          g_tma_2d(sbase + kPOff, &tm.b1[mi], kk * (BK / 8), n0, bar);
         else  // one box of 128 NN rows x 128 B, swizzled: NN consecutive 16 KB operand tiles
-          g_tma_2d(sbase + kBOff, phase1 ? &tm.b1 : &tm.b2, kk * BK, n0, bar);
+          g_tma_2d(sbase + kBOff, phase1 ? &tm.b1[mi] : &tm.b2[mi], kk * BK, n0, bar);
       }
       ++issued;
       if (++st == kStagesG) {
@@ -216,8 +227,8 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         if (ok) {
           const uint32_t sbase = ring + st * kStageG;
           const bool phase2 = it >= p.nk1;
-          const uint32_t lr_off = (phase2 && p.lr_separate) ? BN : 0;
-          const bool first = phase2 ? (p.lr_separate && it == p.nk1) : (it == 0);
+          const uint32_t lr_off = (phase2 && mb.lr_separate) ? BN : 0;
+          const bool first = phase2 ? (mb.lr_separate && it == p.nk1) : (it == 0);
 #pragma unroll
           for (int nn = 0; nn < NN; ++nn) {
 #pragma unroll
@@ -256,7 +267,7 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       const int item = dt + 256 * h;
       rloc[h] = item >> 1;
       half[h] = item & 1;
-      rvalid[h] = (n0 + rloc[h]) < p.OC;
+      rvalid[h] = (n0 + rloc[h]) < mb.OC;
       b_row[h] = (static_cast<uint32_t>(rloc[h]) >> 3) * 1024 + (static_cast<uint32_t>(rloc[h]) & 7) * 128;
       sw[h] = static_cast<uint32_t>(rloc[h]) & 7;
     }
@@ -270,8 +281,8 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       z = 0;
       if (rvalid[h] && G < n_groups && p.w4) {
         const size_t row = static_cast<size_t>(n0 + rloc[h]);
-        sbits = __half_as_ushort(p.scales[row * p.sstride + G]);
-        z = nibble(p.qzeros + row * p.zstride, G);
+        sbits = __half_as_ushort(mb.scales[row * mb.sstride + G]);
+        z = nibble(mb.qzeros + row * mb.zstride, G);
       }
     };
     uint32_t nx_s[NN], nx_z[NN], s2[NN], zlo[NN], zhi[NN];
@@ -339,7 +350,7 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         uint32_t acc[32], lr[32];
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc_col + cb * 32;
         tmem_ld32(taddr, acc);
-        if (NN == 1 && p.lr_separate) tmem_ld32(taddr + BN, lr);
+        if (NN == 1 && mb.lr_separate) tmem_ld32(taddr + BN, lr);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const int c0 = n0 + nn * BN + cb * 32;
         if (ok && tok < p.M) {
@@ -347,21 +358,21 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             v[j] = __uint_as_float(acc[j]);
-            if (NN == 1 && p.lr_separate) v[j] = fmaf(p.alpha, __uint_as_float(lr[j]), v[j]);
-            if (p.bias && c0 + j < p.OC) v[j] += __half2float(p.bias[c0 + j]);
+            if (NN == 1 && mb.lr_separate) v[j] = fmaf(mb.alpha, __uint_as_float(lr[j]), v[j]);
+            if (mb.bias && c0 + j < mb.OC) v[j] += __half2float(mb.bias[c0 + j]);
           }
           if (p.out_fp32) {
-            float* o = static_cast<float*>(p.out) + static_cast<size_t>(tok) * p.out_stride + c0;
-            if (p.out_vec_ok && c0 + 32 <= p.OC) {
+            float* o = static_cast<float*>(mb.out) + static_cast<size_t>(tok) * mb.out_stride + c0;
+            if (mb.out_vec_ok && c0 + 32 <= mb.OC) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
             } else {
               for (int j = 0; j < 32; ++j)
-                if (c0 + j < p.OC) o[j] = v[j];
+                if (c0 + j < mb.OC) o[j] = v[j];
             }
           } else {
-            __half* o = static_cast<__half*>(p.out) + static_cast<size_t>(tok) * p.out_stride + c0;
-            if (p.out_vec_ok && c0 + 32 <= p.OC) {
+            __half* o = static_cast<__half*>(mb.out) + static_cast<size_t>(tok) * mb.out_stride + c0;
+            if (mb.out_vec_ok && c0 + 32 <= mb.OC) {
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
                 uint4 pk;
@@ -378,7 +389,7 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
               }
             } else {
               for (int j = 0; j < 32; ++j)
-                if (c0 + j < p.OC) o[j] = __float2half_rn(v[j]);
+                if (c0 + j < mb.OC) o[j] = __float2half_rn(v[j]);
             }
           }
         }
@@ -407,7 +418,9 @@ cudaError_t launch_gemm_nn(const GemmParams& p, const GemmMaps& tm, cudaStream_t
     if (e != cudaSuccess) return e;
     attr_done[dev] = true;
   }
-  dim3 grid(cdiv(p.OC, BN * NN), cdiv(p.M, BM * p.mt));
+  int n_tiles = 0;
+  for (int i = 0; i < p.n_members; ++i) n_tiles = std::max(n_tiles, p.mem[i].tile_begin + cdiv(p.mem[i].OC, BN * NN));
+  dim3 grid(n_tiles, cdiv(p.M, BM * p.mt));
   gemm_w4a16_kernel<NN><<<grid, kGemmThreads, Cfg<NN>::kSmem, stream>>>(p, tm);
   return cudaGetLastError();
 }
@@ -457,26 +470,23 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
     GemmParams p{};
     GemmMaps tm;
     std::memset(&tm, 0, sizeof(tm));
-    tm.a1 = tm_x;
-    const int nn = 1;  // narrow output (rank columns): small tiles, more CTAs
-    p.mt = 1;
-    if ((rc = map(&tm.b1, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.R, g.IC, g.rank, static_cast<uint64_t>(g.R_stride) * 2, BK, BN * nn,
-                  1)))
+    tm.a1 = tm.a2 = tm_x;
+    if ((rc = map(&tm.b1[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.R, g.IC, g.rank, static_cast<uint64_t>(g.R_stride) * 2, BK, BN, 1)))
       return rc;
-    tm.a2 = tm.a1;
-    tm.b2 = tm.b1;
+    tm.b2[0] = tm.b1[0];
     p.status = status;
-    p.out = g.r_buf;
     p.M = g.M;
-    p.OC = g.rank;
     p.nk1 = cdiv(g.IC, BK);
-    p.nk2 = 0;
     p.w4 = 0;
-    p.out_stride = g.rank;
     p.out_fp32 = 0;
-    p.alpha = 1.f;
-    p.out_vec_ok = 1;  // rank % 8 == 0 and r_buf aligned
-    cudaError_t e = launch_gemm(p, tm, nn, stream);
+    p.n_members = 1;
+    p.mt = 1;  // narrow output (rank columns): small tiles, more CTAs
+    p.mem[0].out = g.r_buf;
+    p.mem[0].OC = g.rank;
+    p.mem[0].out_stride = g.rank;
+    p.mem[0].alpha = 1.f;
+    p.mem[0].out_vec_ok = 1;  // rank % 8 == 0 and r_buf aligned
+    cudaError_t e = launch_gemm(p, tm, 1, stream);
     if (e != cudaSuccess) {
       *cuda_err = e;
       return GLOWQ_ERR_CUDA;
@@ -488,67 +498,78 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
       (rc = map(&tm_r, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.r_buf, g.rank, g.M, static_cast<uint64_t>(g.rank) * 2, BK, BM, 1)))
     return rc;
 
+  // All members in ONE launch: the grid's x index runs over the column tiles of member 0, then member 1, ...
+  bool any_separate = false;
+  for (int i = 0; i < g.n_members; ++i) {
+    const auto& m = g.members[i];
+    any_separate = any_separate || (g.r_mode != GLOWQ_R_NONE && m.L && m.alpha != 0.f && m.alpha != 1.f);
+  }
+  // Tile shape: the 256 x 256 CTA tile has the best operand reuse, but a problem that fills the SMs badly in whole
+  // waves is faster with narrower (nn = 1) or shorter (mt = 1) tiles.  A separate correction accumulator needs nn = 1.
+  int nn = 1, mt = 2;
+  {
+    int sms = 148, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    double best = -1.0;
+    for (int cnn = any_separate ? 1 : 2; cnn >= 1; --cnn)
+      for (int cmt = 2; cmt >= 1; --cmt) {
+        long tiles = 0;
+        for (int i = 0; i < g.n_members; ++i) tiles += cdiv(g.members[i].OC, BN * cnn);
+        tiles *= cdiv(g.M, BM * cmt);
+        const double wave_eff = static_cast<double>(tiles) / (static_cast<double>(cdiv(static_cast<int>(tiles), sms)) * sms);
+        const double reuse = (cnn == 2 ? 1.0 : 0.8) * (cmt == 2 ? 1.0 : 0.65);  // mt = 1 doubles the dequant work per flop
+        if (wave_eff * reuse > best) {
+          best = wave_eff * reuse;
+          nn = cnn;
+          mt = cmt;
+        }
+      }
+  }
+  GemmParams p{};
+  GemmMaps tm;
+  std::memset(&tm, 0, sizeof(tm));
+  tm.a1 = tm_x;
+  tm.a2 = any_corr ? tm_r : tm_x;
+  p.status = status;
+  p.M = g.M;
+  p.nk1 = cdiv(g.IC, BK);
+  p.w4 = 1;
+  p.out_fp32 = g.out_dtype == GLOWQ_OUT_F32;
+  p.n_members = g.n_members;
+  p.mt = mt;
+  int tile_begin = 0;
   for (int i = 0; i < g.n_members; ++i) {
     const auto& m = g.members[i];
     const bool corr = g.r_mode != GLOWQ_R_NONE && m.L && m.alpha != 0.f;
-    const bool lr_separate = corr && m.alpha != 1.f;
-    // Tile shape per launch: the 256 x 256 CTA tile has the best operand reuse, but a problem that fills the SMs
-    // badly in whole waves is faster with narrower (nn = 1) or shorter (mt = 1) tiles.
-    int nn = 1, mt = 2;
-    {
-      int sms = 148;
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
-      double best = -1.0;
-      const int nn_max = (!lr_separate && m.OC >= 2 * BN) ? 2 : 1;
-      for (int cnn = nn_max; cnn >= 1; --cnn)
-        for (int cmt = 2; cmt >= 1; --cmt) {
-          const long tiles = static_cast<long>(cdiv(m.OC, BN * cnn)) * cdiv(g.M, BM * cmt);
-          const double wave_eff = static_cast<double>(tiles) / (static_cast<double>(cdiv(static_cast<int>(tiles), sms)) * sms);
-          const double reuse = (cnn == 2 ? 1.0 : 0.85) * (cmt == 2 ? 1.0 : 0.88);
-          if (wave_eff * reuse > best) {
-            best = wave_eff * reuse;
-            nn = cnn;
-            mt = cmt;
-          }
-        }
-    }
-    GemmParams p{};
-    GemmMaps tm;
-    std::memset(&tm, 0, sizeof(tm));
-    tm.a1 = tm_x;
-    if ((rc = map(&tm.b1, CU_TENSOR_MAP_DATA_TYPE_INT32, m.qweight, static_cast<uint64_t>(G) * 16, m.OC,
+    if ((rc = map(&tm.b1[i], CU_TENSOR_MAP_DATA_TYPE_INT32, m.qweight, static_cast<uint64_t>(G) * 16, m.OC,
                   static_cast<uint64_t>(m.weight_stride_i32) * 4, BK / 8, BN * nn, 0)))
       return rc;
-    tm.a2 = corr ? tm_r : tm_x;
-    tm.b2 = tm.b1;
-    if (corr &&
-        (rc = map(&tm.b2, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, m.L, g.rank, m.OC, static_cast<uint64_t>(m.L_stride) * 2, BK, BN * nn,
-                  1)))
+    tm.b2[i] = tm.b1[i];
+    if (corr && (rc = map(&tm.b2[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, m.L, g.rank, m.OC,
+                          static_cast<uint64_t>(m.L_stride) * 2, BK, BN * nn, 1)))
       return rc;
-    p.scales = static_cast<const __half*>(m.scales);
-    p.qzeros = m.qzeros;
-    p.bias = static_cast<const __half*>(m.bias);
-    p.out = m.out;
-    p.status = status;
-    p.M = g.M;
-    p.OC = m.OC;
-    p.nk1 = cdiv(g.IC, BK);
-    p.nk2 = corr ? cdiv(g.rank, BK) : 0;
-    p.w4 = 1;
-    p.sstride = m.scale_stride;
-    p.zstride = m.zero_stride_i32;
-    p.out_stride = m.out_stride;
-    p.out_fp32 = g.out_dtype == GLOWQ_OUT_F32;
-    p.alpha = m.alpha;
-    p.lr_separate = lr_separate;
-    p.mt = mt;
+    GemmMember& d = p.mem[i];
+    d.scales = static_cast<const __half*>(m.scales);
+    d.qzeros = m.qzeros;
+    d.bias = static_cast<const __half*>(m.bias);
+    d.out = m.out;
+    d.OC = m.OC;
+    d.nk2 = corr ? cdiv(g.rank, BK) : 0;
+    d.sstride = m.scale_stride;
+    d.zstride = m.zero_stride_i32;
+    d.out_stride = m.out_stride;
+    d.alpha = m.alpha;
+    d.lr_separate = corr && m.alpha != 1.f;
     const int esz = p.out_fp32 ? 4 : 2;
-    p.out_vec_ok = al16(m.out) && ((static_cast<size_t>(m.out_stride) * esz) % 16 == 0);
-    cudaError_t e = launch_gemm(p, tm, nn, stream);
-    if (e != cudaSuccess) {
-      *cuda_err = e;
-      return GLOWQ_ERR_CUDA;
-    }
+    d.out_vec_ok = al16(m.out) && ((static_cast<size_t>(m.out_stride) * esz) % 16 == 0);
+    d.tile_begin = tile_begin;
+    tile_begin += cdiv(m.OC, BN * nn);
+  }
+  cudaError_t e = launch_gemm(p, tm, nn, stream);
+  if (e != cudaSuccess) {
+    *cuda_err = e;
+    return GLOWQ_ERR_CUDA;
   }
   return GLOWQ_OK;
 }
