@@ -25,6 +25,9 @@ sys.path.insert(0, ROOT)
 # mean DRAM bytes (read + write) per gemv_stream_kernel launch of the Llama-3.2-3B batch-1 token step, from ncu
 NCU_DRAM_BYTES_PER_LAUNCH = 14.38e6
 
+# decode-sized vectors go through the one-CTA peer-store all-reduce; anything larger (prefill) through NCCL
+PEER_AR_MAX_ELEMS = 64 * 1024
+
 METRIC = "decode_tok_s"
 UNIT = "tokens/s"
 
@@ -42,6 +45,9 @@ def parse_args():
     ap.add_argument("--graph-collectives", action="store_true",
                     help="with N > 1, capture the NCCL all-reduces into the CUDA graph too (default: graphs per segment, "
                          "all-reduces launched between them)")
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                    help="with N > 1: the library's peer-store all-reduce inside one CUDA graph per step (default), or "
+                         "NCCL all-reduces between per-segment graphs")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--unfused", action="store_true", help="one launch per module (wrapper protocol) instead of per group")
@@ -262,6 +268,16 @@ def run_gpu(args, shape):
                 pts.append(idx)
         return pts
 
+    peer_ar = None
+    if world > 1 and args.collective == "peer":
+        try:
+            from glowq_b200.tp import PeerAllReduce
+            peer_ar = PeerAllReduce(dist.group.WORLD, dev, max_elems=PEER_AR_MAX_ELEMS)
+            log("peer all-reduce ready")
+        except Exception as exc:  # noqa: BLE001 - symmetric memory unavailable: fall back to NCCL
+            print(f"[bench] peer all-reduce unavailable ({exc!r}); using NCCL", file=sys.stderr, flush=True)
+            peer_ar = None
+
     def make_step(p):
         """(callable that enqueues one step, list of segments).  With one rank a step is one C call; with N ranks it is
         a list of (group calls, tensor to all-reduce) segments ending at the row-split linears."""
@@ -279,6 +295,13 @@ def run_gpu(args, shape):
             arr = (K.Group * (e - start))(*[p["calls"][i] for i in range(start, e)])
             segs.append((arr, e - start, ptr2t[p["calls"][e - 1].members[0].out]))
             start = e
+
+        if peer_ar is not None and all(t.numel() <= PEER_AR_MAX_ELEMS for _, _, t in segs):
+            def step():
+                for i, (arr, n, t) in enumerate(segs):
+                    stack.ext.check(stack.ext.lib.glowq_w4a16_group_forward_many(arr, n), "group_forward_many")
+                    peer_ar.all_reduce(t, site=i & 1)
+            return step, None          # plain kernels only: the whole step goes into one CUDA graph
 
         def step():
             for arr, n, t in segs:
@@ -408,6 +431,8 @@ def run_gpu(args, shape):
             "vs_baseline": None, "dtype": "f32 accumulate over fp16 x int4 (tensor-core MMA), fp16 out",
             "data": "synthetic",
             "config": workload_config(args, shape, {"parallelism": f"tp{world}", "cuda_graph": use_graph,
+                                                    "collective": ("peer-store all-reduce kernel" if peer_ar is not None
+                                                                   else "nccl") if world > 1 else None,
                                                     "launches_per_layer": calls_per_layer}),
             "clocks": {k: clocks.get(k) for k in ("sm_mhz", "sm_max_mhz", "reasons")},
             "e2e": {"value": M / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -41,10 +41,19 @@ class Group(ctypes.Structure):
                 ("members", Member * MAX_MEMBERS)]
 
 
+MAX_RANKS = 8
+
+
+class Peers(ctypes.Structure):
+    _fields_ = [("buf", ctypes.c_void_p * MAX_RANKS), ("flag", ctypes.c_void_p * MAX_RANKS), ("epoch", ctypes.c_void_p),
+                ("status", ctypes.c_void_p), ("world", ctypes.c_int32), ("rank", ctypes.c_int32),
+                ("sites", ctypes.c_int32), ("max_n", ctypes.c_int32)]
+
+
 EXPORTS = ("glowq_w4a16_version", "glowq_w4a16_strerror", "glowq_w4a16_last_cuda_error", "glowq_w4a16_dequant",
            "glowq_w4a16_gemv_forward", "glowq_w4a16_gemm_forward", "glowq_w4a16_group_forward",
            "glowq_w4a16_group_forward_many", "glowq_w4a16_group_forward_host", "glowq_w4a16_workspace_bytes",
-           "glowq_w4a16_read_status", "glowq_w4a16_gemv_forward_static")
+           "glowq_w4a16_read_status", "glowq_w4a16_gemv_forward_static", "glowq_w4a16_allreduce_f16")
 
 
 def library_path() -> str:
@@ -79,6 +88,7 @@ class _Ext:
         lib.glowq_w4a16_workspace_bytes.argtypes = [i32, i32, i32, i32, i32]
         lib.glowq_w4a16_read_status.argtypes = [vp, vp]
         lib.glowq_w4a16_gemv_forward_static.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]
+        lib.glowq_w4a16_allreduce_f16.argtypes = [ctypes.POINTER(Peers), vp, i32, i32, vp]
         if lib.glowq_w4a16_version() != ABI_VERSION:
             raise RuntimeError("libglowq_w4a16.so ABI version mismatch; rebuild with `python -m glowq_b200.build`")
         self._ws = {}

@@ -82,3 +82,59 @@ def row_parallel_shard(mod: CudaW4A16Linear, rank: int, world: int, R: Optional[
         out.bias.data.copy_(mod.bias.data)
     R_local = None if R is None else R[:, c0:c0 + in_local].contiguous()
     return out, R_local, (c0, c0 + in_local)
+
+
+class PeerAllReduce:
+    """Sum small fp16 tensors across the ranks of one node with the library's peer-store all-reduce
+    (``glowq_w4a16_allreduce_f16``): no NCCL call, so the collective can sit inside a captured CUDA graph.
+
+    Staging buffers and epoch flags live in torch symmetric memory (one allocation per rank, mapped into every peer);
+    PyTorch only provides the mapping - the data movement is the library's kernel.  Two "sites" are used alternately,
+    which is enough for a site never to be rewritten while a slower rank still reads it (a rank can only be two
+    calls ahead of another after that rank has finished the call in between)."""
+
+    SITES = 2
+
+    def __init__(self, group, device, max_elems: int):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        from .cuda_w4a16 import kernels as K
+
+        self.ext = K.load_w4a16_extension()
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > K.MAX_RANKS:
+            raise ValueError(f"at most {K.MAX_RANKS} ranks")
+        self.max_n = (int(max_elems) + 7) // 8 * 8
+        flag_bytes = 256 * ((self.SITES * self.world * 4 + 255) // 256)
+        buf_bytes = self.SITES * self.world * self.max_n * 2
+        self.mem = symm.empty(flag_bytes + buf_bytes, dtype=torch.uint8, device=device)
+        self.mem.zero_()
+        self.handle = symm.rendezvous(self.mem, group)
+        self.local = torch.zeros(64, dtype=torch.int32, device=device)   # [0:SITES] epochs, [32] status
+        self.peers = K.Peers()
+        ptrs = list(self.handle.buffer_ptrs)
+        for r in range(self.world):
+            self.peers.flag[r] = ptrs[r]
+            self.peers.buf[r] = ptrs[r] + flag_bytes
+        self.peers.epoch = self.local.data_ptr()
+        self.peers.status = self.local.data_ptr() + 32 * 4
+        self.peers.world, self.peers.rank = self.world, self.rank
+        self.peers.sites, self.peers.max_n = self.SITES, self.max_n
+        self._calls = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group)          # every rank's flags are zero before anybody's first store arrives
+
+    def all_reduce(self, t: torch.Tensor, site: int = None) -> torch.Tensor:
+        """In-place sum of a contiguous fp16 tensor (numel % 8 == 0) on the current stream."""
+        if t.dtype != torch.float16 or not t.is_contiguous() or t.numel() % 8:
+            raise ValueError("expected a contiguous fp16 tensor with a multiple of 8 elements")
+        if site is None:
+            site = self._calls % self.SITES
+            self._calls += 1
+        rc = self.ext.lib.glowq_w4a16_allreduce_f16(self.peers, t.data_ptr(), t.numel(), int(site),
+                                                    torch.cuda.current_stream(t.device).cuda_stream)
+        self.ext.check(rc, "glowq_w4a16_allreduce_f16")
+        return t
+
+    def status(self) -> int:
+        return int(self.local[32].item())

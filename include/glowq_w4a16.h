@@ -168,6 +168,27 @@ int glowq_w4a16_gemv_forward_static(const void* x, const int32_t* qweight, const
                                     void* out, int M, int IC, int OC, int group_size, int weight_stride_i32,
                                     int zero_stride_i32, int scale_stride, void* stream);
 
+/* Tensor-parallel decode: sum a small fp16 vector (the [M, hidden] output of a row-split o_proj / down_proj) over
+ * the ranks of one NVLink domain with plain peer stores - no NCCL call, so a token step can be replayed from one
+ * CUDA graph.  The reference has no multi-GPU path; this implements the all-reduce point of the tensor-parallel
+ * layout (row-split linears) that the benchmark configurations prescribe.
+ *
+ * Every rank owns a staging buffer of sites * world * max_n fp16 and sites * world uint32 epoch flags, both zeroed
+ * once and mapped into every other rank (e.g. torch symmetric memory); `buf[r]` / `flag[r]` are rank r's, as seen
+ * from this process.  `epoch` (sites uint32, zeroed once) and `status` (one uint32) are local device memory.  All
+ * ranks must make the same sequence of calls per `site`; a site must not be reused before every rank has finished
+ * its previous call on it (two sites used alternately are enough).  `inout`: n fp16 values, n % 8 == 0, 16-byte
+ * aligned, replaced by the sum.  A rank that waits too long for a peer records status 4 and returns. */
+#define GLOWQ_MAX_RANKS 8
+typedef struct glowq_w4a16_peers {
+  void* buf[GLOWQ_MAX_RANKS];
+  void* flag[GLOWQ_MAX_RANKS];
+  void* epoch;
+  void* status;
+  int32_t world, rank, sites, max_n;
+} glowq_w4a16_peers_t;
+int glowq_w4a16_allreduce_f16(const glowq_w4a16_peers_t* peers, void* inout, int n, int site, void* stream);
+
 /* Bytes of workspace a group call with these sizes needs (sync words + split-K partial sums). */
 size_t glowq_w4a16_workspace_bytes(int M, int IC, int OC_total, int rank, int n_members);
 

@@ -1,0 +1,77 @@
+"""The peer-store all-reduce against NCCL on two GPUs (skipped on a single-GPU box)."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    from glowq_b200.tp import PeerAllReduce
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        ar = PeerAllReduce(dist.group.WORLD, dev, max_elems=4 * 3072)
+        gen = torch.Generator(device=dev).manual_seed(100 + rank)
+        worst = 0.0
+        for it in range(40):
+            n = (3072, 8 * 3072 // 8, 4 * 3072, 8)[it % 4]
+            x = torch.randn(n, generator=gen, device=dev).half()
+            want = x.float().clone()
+            dist.all_reduce(want)
+            got = ar.all_reduce(x.clone())
+            torch.cuda.synchronize()
+            worst = max(worst, float((got.float() - want).abs().max()))
+        # replay from a CUDA graph: the collective is an ordinary kernel
+        x = torch.randn(3072, generator=gen, device=dev).half()
+        keep = x.clone()
+        want = x.float().clone()
+        dist.all_reduce(want)
+        s = torch.cuda.Stream(dev)
+        with torch.cuda.stream(s):
+            ar.all_reduce(x, site=0)
+            ar.all_reduce(x, site=1)
+            s.synchronize()
+            g = torch.cuda.CUDAGraph()
+            x.copy_(keep)
+            with torch.cuda.graph(g, stream=s):
+                ar.all_reduce(x, site=0)
+            s.synchronize()
+            for _ in range(3):
+                x.copy_(keep)
+                g.replay()
+            s.synchronize()
+        worst = max(worst, float((x.float() - want).abs().max()))
+        q.put((rank, worst, ar.status()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_allreduce_matches_nccl():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, worst, status in res:
+        assert status == 0, (rank, status)
+        assert worst <= 2e-2, (rank, worst)       # fp16 rounding of a sum of two O(1) values
