@@ -18,6 +18,7 @@
 // The same kernel with an fp16 B operand by TMA (no dequant warps' work) computes r = X . R^T.
 // Every mbarrier wait is bounded; on expiry a status word is set and the CTA drains and frees its tensor memory.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 #include "../../include/glowq_w4a16.h"
@@ -31,6 +32,9 @@ int tensor_map_2d_ex(CUtensorMap* out, CUtensorMapDataType dtype, const void* pt
 
 namespace {
 
+#ifndef GLOWQ_GEMM_PASS_GROUPS
+#define GLOWQ_GEMM_PASS_GROUPS 2
+#endif
 constexpr int BM = 128;   // tokens per accumulator (MMA M)
 constexpr int MT = 2;     // accumulators per CTA
 constexpr int BN = 128;   // output columns per CTA (MMA N)
@@ -42,16 +46,25 @@ constexpr int kPBytes = BN * (BK / 8) * 4;  // 4 KB packed per 128 output column
 // per 256 output columns) and needs all 512 TMEM columns for its four accumulators, so the correction must
 // accumulate in place (alpha == 1); NN = 1 keeps a separate correction accumulator for any alpha.
 template <int NN> struct Cfg {
-  static constexpr int kStages = NN == 2 ? 3 : 4;
-  static constexpr int kStage = MT * kABytes + NN * (kBBytes + kPBytes);
-  static constexpr int kSmem = 2048 + kStages * kStage;  // 1 KB alignment slack + 1 KB of barriers + the ring
+  static constexpr int kMaxStages = 8;
+  // dequant (then epilogue) warps: one thread per half-row (32 columns) of the step's 128 NN-row packed tile.  The
+  // dequantisation is the slower side of the pipeline at large M, and it is latency-bound: more warps, not wider ones.
+  static constexpr int kDequantWarps = 8 * NN;
+  static constexpr int kThreads = 64 + 32 * kDequantWarps;
+  // The dequant warps work in kPassGroups teams; team g converts the packed tiles of steps g, g + kPassGroups, ...
+  // (each thread then covers kPassGroups half-rows of a step), so that the fixed latency of a pass - barrier wake-up,
+  // shared-memory round trip, proxy fence - overlaps between consecutive steps instead of adding up.
+  static constexpr int kPassGroups = GLOWQ_GEMM_PASS_GROUPS;
+  // A stage holds mt activation tiles, NN operand tiles and NN packed tiles; the ring is as deep as 227 KB allow
+  // (3 stages for the 256 x 256 tile, 4 for 128 x 256, 6 for 128 x 128): narrow launches are bound by the latency
+  // of the weight stream, which only depth hides.
+  static constexpr int stage_bytes(int mt) { return mt * kABytes + NN * (kBBytes + kPBytes); }
+  static constexpr int kSmemMax = 227 * 1024 - 256;  // the kernel also has a few bytes of static shared memory
+  static int stages(int mt) { return std::min(kMaxStages, (kSmemMax - 2048) / stage_bytes(mt)); }
+  static int smem(int mt) { return 2048 + stages(mt) * stage_bytes(mt); }  // 1 KB alignment slack + 1 KB of barriers + ring
 };
-constexpr int kDequantWarps = 8;  // two threads per B-tile row: a single warp per scheduler is latency-bound
-constexpr int kGemmThreads = 64 + 32 * kDequantWarps;
 constexpr uint32_t kGemmSpin = 1u << 18;
 constexpr uint32_t kTmemCols = 512;
-// instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = 128, M = 128
-constexpr uint32_t kIdesc = (1u << 4) | ((BN >> 3) << 17) | ((BM >> 4) << 24);
 
 struct GemmMember {   // one linear of the group; its column tiles are blockIdx.x in [tile_begin, next tile_begin)
   const __half* scales;
@@ -65,6 +78,13 @@ struct GemmParams {
   uint32_t* status;
   int M, nk1, w4, out_fp32, n_members;
   int mt;  // 128-token accumulators per CTA actually used (1 or 2): 1 spreads a narrow product over more CTAs
+  int stages;  // ring depth for this mt
+  // split-K (only the narrow r = X . R^T product uses it): gridDim.z CTAs share a tile's K steps, each writes its fp32
+  // partial tile to its own slot, and the last one to arrive adds the slots in order and stores the result
+  int ksplit;
+  int debug;         // tuning experiments only (0 in production): 16 no copies after the first ring round, 32 no MMA, 64 no dequant
+  float* slots;      // [ksplit][tiles][NN * MT * 128 * 128]
+  uint32_t* kctr;    // [tiles] arrival counters, zero between launches
   GemmMember mem[kMaxMembers];
 };
 struct alignas(64) GemmMaps {
@@ -82,8 +102,17 @@ __device__ __forceinline__ void g_mbar_arrive(uint32_t a) {
 __device__ __forceinline__ void g_mbar_expect_tx(uint32_t a, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool g_mbar_wait(uint32_t a, uint32_t parity, volatile int* abort_flag, uint32_t* status) {
+__device__ __forceinline__ bool g_mbar_wait(uint32_t a, uint32_t parity, volatile int* abort_flag, uint32_t* status,
+                                            int spin_first = 0) {
   uint32_t spins = 0;
+  for (int i = 0; i < spin_first; ++i) {  // non-suspending polls first: a wait that is about to succeed stays awake
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(a), "r"(parity)
+                 : "memory");
+    if (ok) return true;
+  }
   for (;;) {
     uint32_t ok;
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
@@ -110,12 +139,37 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
   return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(1) << 16) |
          (static_cast<uint64_t>(1024 >> 4) << 32) | (static_cast<uint64_t>(1) << 46) | (static_cast<uint64_t>(2) << 61);
 }
+template <int N>
 __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+  // instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, M = 128, N columns
+  constexpr uint32_t kIdesc = (1u << 4) | ((static_cast<uint32_t>(N) >> 3) << 17) | ((BM >> 4) << 24);
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate), "r"(0u)
       : "memory");
+}
+template <int N>
+__device__ __forceinline__ void umma_f16_acc(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc) {  // D += A . B
+  constexpr uint32_t kIdesc = (1u << 4) | ((static_cast<uint32_t>(N) >> 3) << 17) | ((BM >> 4) << 24);
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.eq.b32 p, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(kIdesc)
+      : "memory");
+}
+__device__ __forceinline__ uint64_t mk64(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ bool g_mbar_try_once(uint32_t a, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok)
+               : "r"(a), "r"(parity)
+               : "memory");
+  return ok != 0;
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -132,17 +186,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 
 template <int NN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(Cfg<NN>::kThreads, 1)
 gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ GemmMaps tm) {
-  constexpr int kStagesG = Cfg<NN>::kStages;
-  constexpr int kStageG = Cfg<NN>::kStage;
-  constexpr int kBOff = MT * kABytes;                 // B tiles inside a stage
-  constexpr int kPOff = MT * kABytes + NN * kBBytes;  // packed tiles inside a stage
+  const int kStagesG = p.stages;
+  const uint32_t kBOff = p.mt * kABytes;            // B tiles inside a stage
+  const uint32_t kPOff = kBOff + NN * kBBytes;      // packed tiles inside a stage
+  const uint32_t kStageG = kPOff + NN * kPBytes;
   extern __shared__ unsigned char smem[];
   __shared__ int s_abort;
   __shared__ uint32_t s_tmem_base;
   const uint32_t smem0 = (sm_u32(smem) + 1023u) & ~1023u;  // swizzled operand tiles want 1024-byte alignment
-  // barriers live in the first 1 KB: full[4], empty[4], bready[4], accum
+  // barriers live in the first 1 KB: full[8], empty[8], bready[8], accum
   const uint32_t full_b = smem0, empty_b = smem0 + 64, bready_b = smem0 + 128, accum_b = smem0 + 192;
   const uint32_t ring = smem0 + 1024;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -154,14 +208,16 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   const int n0 = (static_cast<int>(blockIdx.x) - mb.tile_begin) * (BN * NN), m0 = blockIdx.y * (BM * p.mt);
   const int n_mt = (p.mt == 2 && m0 + BM < p.M) ? 2 : 1;
   const int n_nt = (NN == 2 && n0 + BN < mb.OC) ? 2 : 1;
-  const int nk = p.nk1 + mb.nk2;
+  const int nk_all = (p.debug & 1024) ? (p.nk1 + mb.nk2) / 4 : p.nk1 + mb.nk2;
+  const int it0 = p.ksplit > 1 ? static_cast<int>(static_cast<long long>(nk_all) * blockIdx.z / p.ksplit) : 0;
+  const int nk = p.ksplit > 1 ? static_cast<int>(static_cast<long long>(nk_all) * (blockIdx.z + 1) / p.ksplit) : nk_all;
 
   if (threadIdx.x == 0) {
     s_abort = 0;
     for (int i = 0; i < kStagesG; ++i) {
       g_mbar_init(full_b + 8 * i, 1);
       g_mbar_init(empty_b + 8 * i, 1);
-      g_mbar_init(bready_b + 8 * i, kDequantWarps);
+      g_mbar_init(bready_b + 8 * i, Cfg<NN>::kDequantWarps / Cfg<NN>::kPassGroups);
     }
     g_mbar_init(accum_b, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -176,105 +232,133 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = s_tmem_base;
   volatile int* abort_flag = &s_abort;
+  // debug & 2048: CTA 0 records clock64() per role / event / step at workspace + 4096 (tuning only)
+  unsigned long long* trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(p.status) - WS_STATUS * 4 + 4096);
+  const bool tracing = (p.debug & 2048) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
+  auto tr = [&](int role, int ev, int step) {
+    if (tracing && step < 256) trace[(role * 3 + ev) * 256 + step] = clock64();
+  };
+  const int spin1 = (p.debug & 128) ? 4096 : 0, spin2 = (p.debug & 256) ? 256 : 0;
 
   if (warp == 0) {
-    // ================================================================ TMA producer
-    uint32_t st = 0, ph = 0;
-    int issued = 0;
-    bool ok = true;
-    for (int it = 0; it < nk && ok; ++it) {
-      if (!(ok = g_mbar_wait(empty_b + 8 * st, ph ^ 1, abort_flag, p.status))) break;
-      if (lane == 0) {
+    // ================================================================ TMA producer (one thread: a wait that the
+    // whole warp executes costs 32 serialised barrier operations)
+    if (lane == 0) {
+      uint32_t st = 0, ph = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int it = it0; it < nk && ok; ++it) {
+        tr(0, 0, it - it0);
+        if (!(ok = g_mbar_wait(empty_b + 8 * st, ph ^ 1, abort_flag, p.status, spin1))) break;
+        tr(0, 1, it - it0);
         const uint32_t sbase = ring + st * kStageG, bar = full_b + 8 * st;
         const bool phase1 = it < p.nk1;
         const int kk = phase1 ? it : it - p.nk1;
         const bool packed = phase1 && p.w4;
-        g_mbar_expect_tx(bar, n_mt * kABytes + NN * (packed ? kPBytes : kBBytes));
-        const CUtensorMap* ta = phase1 ? &tm.a1 : &tm.a2;
-        g_tma_2d(sbase, ta, kk * BK, m0, bar);
-        if (n_mt == 2) g_tma_2d(sbase + kABytes, ta, kk * BK, m0 + BM, bar);
-        if (packed)  // one box of 128 NN rows x 32 B
-          g_tma_2d(sbase + kPOff, &tm.b1[mi], kk * (BK / 8), n0, bar);
-        else  // one box of 128 NN rows x 128 B, swizzled: NN consecutive 16 KB operand tiles
-          g_tma_2d(sbase + kBOff, phase1 ? &tm.b1[mi] : &tm.b2[mi], kk * BK, n0, bar);
+        if ((p.debug & 16) && it - it0 >= kStagesG) {
+          g_mbar_arrive(bar);
+        } else {
+          g_mbar_expect_tx(bar, n_mt * kABytes + NN * (packed ? kPBytes : kBBytes));
+          const CUtensorMap* ta = phase1 ? &tm.a1 : &tm.a2;
+          g_tma_2d(sbase, ta, kk * BK, m0, bar);
+          if (n_mt == 2) g_tma_2d(sbase + kABytes, ta, kk * BK, m0 + BM, bar);
+          if (packed)  // one box of 128 NN rows x 32 B
+            g_tma_2d(sbase + kPOff, &tm.b1[mi], kk * (BK / 8), n0, bar);
+          else  // one box of 128 NN rows x 128 B, swizzled: NN consecutive 16 KB operand tiles
+            g_tma_2d(sbase + kBOff, phase1 ? &tm.b1[mi] : &tm.b2[mi], kk * BK, n0, bar);
+        }
+        ++issued;
+        if (++st == static_cast<uint32_t>(kStagesG)) {
+          st = 0;
+          ph ^= 1;
+        }
       }
-      ++issued;
-      if (++st == kStagesG) {
-        st = 0;
-        ph ^= 1;
+      if (!ok) {  // wait (bounded) for copies that are still in flight
+        for (int j = (issued > kStagesG ? issued - kStagesG : 0); j < issued; ++j) {
+          uint32_t spins = 0, done = 0;
+          while (!done && ++spins < kGemmSpin)
+            asm volatile(
+                "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(done)
+                : "r"(full_b + 8 * (j % kStagesG)), "r"((j / kStagesG) & 1)
+                : "memory");
+        }
       }
     }
-    if (!ok) {  // wait (bounded) for copies that are still in flight
-      for (int j = (issued > kStagesG ? issued - kStagesG : 0); j < issued; ++j) {
-        uint32_t spins = 0, done = 0;
-        while (!done && ++spins < kGemmSpin)
-          asm volatile(
-              "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-              : "=r"(done)
-              : "r"(full_b + 8 * (j % kStagesG)), "r"((j / kStagesG) & 1)
-              : "memory");
-      }
-    }
+    __syncwarp();
   } else if (warp == 1) {
-    // ================================================================ MMA issuer
-    uint32_t st = 0, ph = 0;
-    bool ok = true;
-    for (int it = 0; it < nk; ++it) {
-      ok = ok && g_mbar_wait(full_b + 8 * st, ph, abort_flag, p.status);
-      ok = ok && g_mbar_wait(bready_b + 8 * st, ph, abort_flag, p.status);
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (lane == 0) {
-        if (ok) {
-          const uint32_t sbase = ring + st * kStageG;
+    // ================================================================ MMA issuer (one thread).  The dequant warps
+    // wait for the stage's copies before they arrive on `bready`, so that barrier alone says that A and B are in place.
+    if (lane == 0) {
+      // A single thread runs this loop, so every instruction in it is latency on the critical path: descriptors are
+      // one 32-bit add each (the address field, in 16-byte units, never carries out of the low word).
+      uint32_t st = 0, ph = 0;
+      bool ok = true;
+      const uint64_t desc0 = smem_desc_sw128(ring);
+      const uint32_t desc_hi = static_cast<uint32_t>(desc0 >> 32);
+      uint32_t desc_lo = static_cast<uint32_t>(desc0);
+      const uint32_t desc_lo0 = desc_lo;
+      const uint32_t stage16 = kStageG >> 4, boff16 = kBOff >> 4;
+      const bool skip_mma = (p.debug & 32) != 0;
+      for (int it = it0; it < nk; ++it) {
+        if (ok && !g_mbar_try_once(bready_b + 8 * st, ph)) ok = g_mbar_wait(bready_b + 8 * st, ph, abort_flag, p.status, spin1);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok && !(skip_mma && it > it0)) {
           const bool phase2 = it >= p.nk1;
           const uint32_t lr_off = (phase2 && mb.lr_separate) ? BN : 0;
-          const bool first = phase2 ? (mb.lr_separate && it == p.nk1) : (it == 0);
+          const bool first = phase2 ? (mb.lr_separate && it == p.nk1) : (it == it0);
 #pragma unroll
-          for (int nn = 0; nn < NN; ++nn) {
+          for (int mt = 0; mt < MT; ++mt) {
+            if (mt < n_mt) {
+              // NN = 2: one N = 256 instruction covers both operand tiles (they are consecutive 8-row atoms)
+              const uint32_t acc_col = (NN == 1) ? mt * (2 * BN) + lr_off : mt * (NN * BN);
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-              if (mt < n_mt && nn < n_nt) {
-                const uint32_t acc_col = (NN == 1) ? mt * (2 * BN) + lr_off : (nn * MT + mt) * BN;
-#pragma unroll
-                for (int k16 = 0; k16 < BK / 16; ++k16) {
-                  const uint64_t ad = smem_desc_sw128(sbase + mt * kABytes + k16 * 32);
-                  const uint64_t bd = smem_desc_sw128(sbase + kBOff + nn * kBBytes + k16 * 32);
-                  umma_f16(tmem_base + acc_col, ad, bd, (first && k16 == 0) ? 0u : 1u);
-                }
+              for (int k16 = 0; k16 < BK / 16; ++k16) {
+                const uint64_t ad = mk64(desc_lo + (mt * (kABytes >> 4) + k16 * 2), desc_hi);
+                const uint64_t bd = mk64(desc_lo + boff16 + k16 * 2, desc_hi);
+                if (k16 == 0) umma_f16<NN * BN>(tmem_base + acc_col, ad, bd, first ? 0u : 1u);
+                else umma_f16_acc<NN * BN>(tmem_base + acc_col, ad, bd);
               }
             }
           }
         }
-        umma_commit(empty_b + 8 * st);  // the stage is free once the MMAs above have read it
+        if (p.debug & 512) g_mbar_arrive(empty_b + 8 * st);
+        else umma_commit(empty_b + 8 * st);  // the stage is free once the MMAs above have read it
+        tr(1, 2, it - it0);
+        desc_lo += stage16;
+        if (++st == static_cast<uint32_t>(kStagesG)) {
+          st = 0;
+          ph ^= 1;
+          desc_lo = desc_lo0;
+        }
       }
-      __syncwarp();
-      if (++st == kStagesG) {
-        st = 0;
-        ph ^= 1;
-      }
+      umma_commit(accum_b);
     }
-    if (lane == 0) umma_commit(accum_b);
     __syncwarp();
   } else {
     // ================================================================ dequant warps, then epilogue
-    // 256 threads share the 128 NN rows of the step's packed tile: NN half-rows (32 columns) per thread
+    // one thread per half-row (32 columns) of the step's 128 NN-row packed tile
+    constexpr int H = Cfg<NN>::kPassGroups;
+    constexpr int kGroupThreads = Cfg<NN>::kDequantWarps * 32 / H;
     const int dt = threadIdx.x - 64;
-    int rloc[NN], half[NN];
-    bool rvalid[NN];
-    uint32_t b_row[NN], sw[NN];
+    const int pg = dt / kGroupThreads, lt = dt - pg * kGroupThreads;  // pass group, thread within it
+    int rloc[H], half[H];
+    bool rvalid[H];
+    uint32_t b_row[H], sw[H];
 #pragma unroll
-    for (int h = 0; h < NN; ++h) {
-      const int item = dt + 256 * h;
+    for (int h = 0; h < H; ++h) {
+      const int item = lt + h * kGroupThreads;
       rloc[h] = item >> 1;
       half[h] = item & 1;
       rvalid[h] = (n0 + rloc[h]) < mb.OC;
       b_row[h] = (static_cast<uint32_t>(rloc[h]) >> 3) * 1024 + (static_cast<uint32_t>(rloc[h]) & 7) * 128;
       sw[h] = static_cast<uint32_t>(rloc[h]) & 7;
     }
-    uint32_t st = 0, ph = 0;
+    uint32_t st = pg, ph = 0;   // kPassGroups <= ring depth
     bool ok = true;
-    // scale / zero-point of a row: group G is needed at steps 2G and 2G+1; the next group's pair is fetched one
-    // group ahead so that the global-load latency never sits between a stage becoming free and its tile being written
+    // scale / zero-point of a row: quantisation group G covers steps 2G and 2G+1; the pair for the next step this pass
+    // group will handle is fetched one pass ahead, so that the global-load latency never sits between a stage
+    // becoming free and its tile being written
     const int n_groups = (p.nk1 + 1) >> 1;
     auto fetch_sz = [&](int h, int G, uint32_t& sbits, uint32_t& z) {
       sbits = 0;
@@ -285,28 +369,38 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         z = nibble(mb.qzeros + row * mb.zstride, G);
       }
     };
-    uint32_t nx_s[NN], nx_z[NN], s2[NN], zlo[NN], zhi[NN];
+    uint32_t nx_s[H], nx_z[H], s2[H], zlo[H], zhi[H];
 #pragma unroll
-    for (int h = 0; h < NN; ++h) {
-      fetch_sz(h, 0, nx_s[h], nx_z[h]);
+    for (int h = 0; h < H; ++h) {
+      fetch_sz(h, (it0 + pg) >> 1, nx_s[h], nx_z[h]);
       s2[h] = zlo[h] = zhi[h] = 0;
     }
-    for (int it = 0; it < nk; ++it) {
-      ok = ok && g_mbar_wait(empty_b + 8 * st, ph ^ 1, abort_flag, p.status);
-      if (it < p.nk1 && p.w4) {
-        if ((it & 1) == 0) {  // first step of group it/2
+    int cur_g = -1;
+    for (int it = it0 + pg; it < nk; it += H) {
+      if (warp == 2) tr(2, 0, it - it0);
+      if (lane == 0) {  // one lane polls; the stage's copies must have landed before this warp reports the tile ready
+        ok = ok && g_mbar_wait(empty_b + 8 * st, ph ^ 1, abort_flag, p.status, spin2);
+        ok = ok && g_mbar_wait(full_b + 8 * st, ph, abort_flag, p.status, spin2);
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (warp == 2) tr(2, 1, it - it0);
+      if (it < p.nk1 && p.w4 && !(p.debug & 64)) {
+        if ((it >> 1) != cur_g) {  // first step of this pass group in quantisation group it/2
+          cur_g = it >> 1;
 #pragma unroll
-          for (int h = 0; h < NN; ++h) {
+          for (int h = 0; h < H; ++h) {
             s2[h] = nx_s[h] * 0x00010001u;
             zero_consts(nx_z[h], zlo[h], zhi[h]);
-            fetch_sz(h, (it >> 1) + 1, nx_s[h], nx_z[h]);
           }
         }
-        ok = ok && g_mbar_wait(full_b + 8 * st, ph, abort_flag, p.status);
+        if (((it + H) >> 1) != cur_g) {
+#pragma unroll
+          for (int h = 0; h < H; ++h) fetch_sz(h, (it + H) >> 1, nx_s[h], nx_z[h]);
+        }
         if (ok) {
           const uint32_t sbase = ring + st * kStageG;
 #pragma unroll
-          for (int h = 0; h < NN; ++h) {
+          for (int h = 0; h < H; ++h) {
             const uint32_t pbase = sbase + kPOff + rloc[h] * 32 + half[h] * 16;
             uint32_t w[4];
             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(pbase));
@@ -330,8 +424,10 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       }
       __syncwarp();
       if (lane == 0) g_mbar_arrive(bready_b + 8 * st);
-      if (++st == kStagesG) {
-        st = 0;
+      if (warp == 2) tr(2, 2, it - it0);
+      st += H;
+      if (st >= static_cast<uint32_t>(kStagesG)) {
+        st -= kStagesG;
         ph ^= 1;
       }
     }
@@ -340,13 +436,57 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     ok = ok && g_mbar_wait(accum_b, 0, abort_flag, p.status);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int q = warp & 3;                          // TMEM lane quadrant this warp may read
-    const int cb0 = ((warp - 2) >> 2) * (BN / 64);   // warps 2-5 take columns 0..63 of a tile, warps 6-9 columns 64..127
+    constexpr int kWays = Cfg<NN>::kDequantWarps / 4;  // warps that share a lane quadrant split the tile's columns
+    constexpr int kCbPer = (BN / 32) / kWays;
+    const int cb0 = ((warp - 2) >> 2) * kCbPer;
+    // bias, conversion and store of 32 consecutive columns c0.. of token tok
+    auto emit = [&](float (&v)[32], int tok, int c0) {
+      if (mb.bias) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (c0 + j < mb.OC) v[j] += __half2float(mb.bias[c0 + j]);
+      }
+      if (p.out_fp32) {
+        float* o = static_cast<float*>(mb.out) + static_cast<size_t>(tok) * mb.out_stride + c0;
+        if (mb.out_vec_ok && c0 + 32 <= mb.OC) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+          for (int j = 0; j < 32; ++j)
+            if (c0 + j < mb.OC) o[j] = v[j];
+        }
+      } else {
+        __half* o = static_cast<__half*>(mb.out) + static_cast<size_t>(tok) * mb.out_stride + c0;
+        if (mb.out_vec_ok && c0 + 32 <= mb.OC) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 pk;
+            __half2 h;
+            h = __floats2half2_rn(v[j], v[j + 1]);
+            pk.x = *reinterpret_cast<uint32_t*>(&h);
+            h = __floats2half2_rn(v[j + 2], v[j + 3]);
+            pk.y = *reinterpret_cast<uint32_t*>(&h);
+            h = __floats2half2_rn(v[j + 4], v[j + 5]);
+            pk.z = *reinterpret_cast<uint32_t*>(&h);
+            h = __floats2half2_rn(v[j + 6], v[j + 7]);
+            pk.w = *reinterpret_cast<uint32_t*>(&h);
+            *reinterpret_cast<uint4*>(o + j) = pk;
+          }
+        } else {
+          for (int j = 0; j < 32; ++j)
+            if (c0 + j < mb.OC) o[j] = __float2half_rn(v[j]);
+        }
+      }
+    };
+    const size_t kSlotFloats = static_cast<size_t>(NN) * p.mt * BM * BN;
+    const size_t tile_lin = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
+    const size_t n_tiles_all = static_cast<size_t>(gridDim.x) * gridDim.y;
     for (int at = 0; at < NN * MT; ++at) {
       const int nn = at / MT, mt = at - nn * MT;
       if (mt >= n_mt || nn >= n_nt) continue;
       const int tok = m0 + mt * BM + q * 32 + lane;
-      const uint32_t acc_col = (NN == 1) ? mt * (2 * BN) : (nn * MT + mt) * BN;
-      for (int cb = cb0; cb < cb0 + BN / 64; ++cb) {
+      const uint32_t acc_col = (NN == 1) ? mt * (2 * BN) : (mt * NN + nn) * BN;
+      for (int cb = cb0; cb < cb0 + kCbPer; ++cb) {
         uint32_t acc[32], lr[32];
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc_col + cb * 32;
         tmem_ld32(taddr, acc);
@@ -359,40 +499,52 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           for (int j = 0; j < 32; ++j) {
             v[j] = __uint_as_float(acc[j]);
             if (NN == 1 && mb.lr_separate) v[j] = fmaf(mb.alpha, __uint_as_float(lr[j]), v[j]);
-            if (mb.bias && c0 + j < mb.OC) v[j] += __half2float(mb.bias[c0 + j]);
           }
-          if (p.out_fp32) {
-            float* o = static_cast<float*>(mb.out) + static_cast<size_t>(tok) * mb.out_stride + c0;
-            if (mb.out_vec_ok && c0 + 32 <= mb.OC) {
+          if (p.ksplit > 1) {
+            float* sl = p.slots + (static_cast<size_t>(blockIdx.z) * n_tiles_all + tile_lin) * kSlotFloats +
+                        static_cast<size_t>(at) * (BM * BN) + (q * 32 + lane) * BN + cb * 32;
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (c0 + j < mb.OC) o[j] = v[j];
-            }
+            for (int j = 0; j < 32; j += 4) __stcg(reinterpret_cast<float4*>(sl + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
           } else {
-            __half* o = static_cast<__half*>(mb.out) + static_cast<size_t>(tok) * mb.out_stride + c0;
-            if (mb.out_vec_ok && c0 + 32 <= mb.OC) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 pk;
-                __half2 h;
-                h = __floats2half2_rn(v[j], v[j + 1]);
-                pk.x = *reinterpret_cast<uint32_t*>(&h);
-                h = __floats2half2_rn(v[j + 2], v[j + 3]);
-                pk.y = *reinterpret_cast<uint32_t*>(&h);
-                h = __floats2half2_rn(v[j + 4], v[j + 5]);
-                pk.z = *reinterpret_cast<uint32_t*>(&h);
-                h = __floats2half2_rn(v[j + 6], v[j + 7]);
-                pk.w = *reinterpret_cast<uint32_t*>(&h);
-                *reinterpret_cast<uint4*>(o + j) = pk;
-              }
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (c0 + j < mb.OC) o[j] = __float2half_rn(v[j]);
-            }
+            emit(v, tok, c0);
           }
         }
+      }
+    }
+    if (p.ksplit > 1) {  // the last CTA of the tile to get here adds the slots (in slice order: deterministic)
+      __shared__ int s_last;
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"n"(Cfg<NN>::kDequantWarps * 32) : "memory");
+      if (threadIdx.x == 64) s_last = (atomicAdd(p.kctr + tile_lin, 1u) == static_cast<uint32_t>(p.ksplit - 1));
+      asm volatile("bar.sync 1, %0;" ::"n"(Cfg<NN>::kDequantWarps * 32) : "memory");
+      if (s_last) {
+        __threadfence();
+        for (int at = 0; at < NN * MT; ++at) {
+          const int nn = at / MT, mt = at - nn * MT;
+          if (mt >= n_mt || nn >= n_nt) continue;
+          const int tok = m0 + mt * BM + q * 32 + lane;
+          for (int cb = cb0; cb < cb0 + kCbPer; ++cb) {
+            const int c0 = n0 + nn * BN + cb * 32;
+            if (!(ok && tok < p.M)) continue;
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+            for (int z = 0; z < p.ksplit; ++z) {
+              const float* sl = p.slots + (static_cast<size_t>(z) * n_tiles_all + tile_lin) * kSlotFloats +
+                                static_cast<size_t>(at) * (BM * BN) + (q * 32 + lane) * BN + cb * 32;
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                const float4 t = __ldcg(reinterpret_cast<const float4*>(sl + j));
+                v[j] += t.x;
+                v[j + 1] += t.y;
+                v[j + 2] += t.z;
+                v[j + 3] += t.w;
+              }
+            }
+            emit(v, tok, c0);
+          }
+        }
+        if (threadIdx.x == 64) p.kctr[tile_lin] = 0;  // ready for the next launch
       }
     }
   }
@@ -414,14 +566,18 @@ cudaError_t launch_gemm_nn(const GemmParams& p, const GemmMaps& tm, cudaStream_t
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_kernel<NN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NN>::kSmem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_kernel<NN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         std::max(Cfg<NN>::smem(1), Cfg<NN>::smem(2)));
     if (e != cudaSuccess) return e;
     attr_done[dev] = true;
   }
   int n_tiles = 0;
   for (int i = 0; i < p.n_members; ++i) n_tiles = std::max(n_tiles, p.mem[i].tile_begin + cdiv(p.mem[i].OC, BN * NN));
-  dim3 grid(n_tiles, cdiv(p.M, BM * p.mt));
-  gemm_w4a16_kernel<NN><<<grid, kGemmThreads, Cfg<NN>::kSmem, stream>>>(p, tm);
+  GemmParams q = p;
+  q.stages = Cfg<NN>::stages(p.mt);
+  if (q.ksplit < 1) q.ksplit = 1;
+  dim3 grid(n_tiles, cdiv(p.M, BM * p.mt), q.ksplit);
+  gemm_w4a16_kernel<NN><<<grid, Cfg<NN>::kThreads, Cfg<NN>::smem(p.mt), stream>>>(q, tm);
   return cudaGetLastError();
 }
 
@@ -446,7 +602,32 @@ bool gemm_supported(const glowq_w4a16_group_t& g) {
   return true;
 }
 
-size_t gemm_workspace_bytes(int, int, int, int, int) { return kWsHeaderBytes; }
+// K slices of the r = X . R^T product (a [M, rank] output is a handful of tiles: without slicing a few CTAs would
+// walk all of K while the rest of the GPU idles).  Device-independent so that the workspace size is, too.
+constexpr int kKctrWord = 8;                                   // header words [8, 64) hold the tiles' arrival counters
+constexpr int kKctrTiles = WS_HEADER_WORDS - kKctrWord;
+constexpr size_t kRSlotBytes = static_cast<size_t>(BM) * BN * 4;   // slot of an NN = 1, mt = 1 tile
+inline int r_ksplit(int M, int IC, int rank) {
+  const int tiles = cdiv(rank, BN) * cdiv(M, BM), nk = cdiv(IC, BK);
+  if (tiles > kKctrTiles) return 1;
+  return std::max(1, std::min({16, nk / 4, 128 / tiles}));
+}
+
+inline size_t r_slot_bytes(int M, int IC, int rank) {
+  const int ks = r_ksplit(M, IC, rank);
+  return ks > 1 ? static_cast<size_t>(ks) * cdiv(rank, BN) * cdiv(M, BM) * kRSlotBytes : 0;
+}
+// The slots sit at the END of the workspace, clear of the counters that the weight-streaming kernel keeps (zeroed)
+// at its start: one workspace may serve launches of both kernels in turn.
+inline size_t counters_end(int OC_total, int n_members) {
+  const size_t n = kWsHeaderBytes + kMaxRTiles * 4 + (static_cast<size_t>(cdiv(OC_total, kTileRows)) + n_members) * 4;
+  return (n + 255) & ~static_cast<size_t>(255);
+}
+
+size_t gemm_workspace_bytes(int M, int IC, int OC_total, int rank, int n_members) {
+  if (rank <= 0) return kWsHeaderBytes;
+  return counters_end(OC_total, n_members) + r_slot_bytes(M, IC, rank) + 256;
+}
 
 int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaError_t* cuda_err) {
   if (g.workspace_bytes < kWsHeaderBytes) return GLOWQ_ERR_WORKSPACE_TOO_SMALL;
@@ -481,6 +662,17 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
     p.out_fp32 = 0;
     p.n_members = 1;
     p.mt = 1;  // narrow output (rank columns): small tiles, more CTAs
+    p.ksplit = r_ksplit(g.M, g.IC, g.rank);
+    int oc_total = 0;
+    for (int i = 0; i < g.n_members; ++i) oc_total += g.members[i].OC;
+    const size_t slot_bytes = r_slot_bytes(g.M, g.IC, g.rank);
+    size_t slot_off = g.workspace_bytes >= slot_bytes ? ((g.workspace_bytes - slot_bytes) & ~static_cast<size_t>(255)) : 0;
+    if (slot_off < counters_end(oc_total, g.n_members)) {  // workspace not sized for slicing: one CTA per tile walks all of K
+      p.ksplit = 1;
+      slot_off = kWsHeaderBytes;
+    }
+    p.slots = reinterpret_cast<float*>(static_cast<unsigned char*>(g.workspace) + slot_off);
+    p.kctr = static_cast<uint32_t*>(g.workspace) + kKctrWord;
     p.mem[0].out = g.r_buf;
     p.mem[0].OC = g.rank;
     p.mem[0].out_stride = g.rank;
@@ -526,6 +718,12 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
         }
       }
   }
+  {  // tuning overrides (unset in production)
+    static const int env_nn = [] { const char* e = std::getenv("GLOWQ_GEMM_NN"); return e ? std::atoi(e) : 0; }();
+    static const int env_mt = [] { const char* e = std::getenv("GLOWQ_GEMM_MT"); return e ? std::atoi(e) : 0; }();
+    if ((env_nn == 1 || env_nn == 2) && !(any_separate && env_nn == 2)) nn = env_nn;
+    if (env_mt == 1 || env_mt == 2) mt = env_mt;
+  }
   GemmParams p{};
   GemmMaps tm;
   std::memset(&tm, 0, sizeof(tm));
@@ -538,6 +736,7 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
   p.out_fp32 = g.out_dtype == GLOWQ_OUT_F32;
   p.n_members = g.n_members;
   p.mt = mt;
+  p.debug = g.reserved;
   int tile_begin = 0;
   for (int i = 0; i < g.n_members; ++i) {
     const auto& m = g.members[i];

@@ -43,6 +43,7 @@ def main():
     ap.add_argument("--modes", default="plain,corr")
     ap.add_argument("--split-k", type=int, default=0)
     ap.add_argument("--iters", type=int, default=200)
+    ap.add_argument("--debug", type=int, default=0, help="kernel tuning switches (0 in any real measurement)")
     ap.add_argument("--kernel", type=int, default=0, help="0 auto, 1 weight-streaming kernel, 2 tensor-core GEMM")
     args = ap.parse_args()
     ext = K.load_w4a16_extension()
@@ -67,6 +68,7 @@ def main():
                     g = K.Group()
                     g.x, g.M, g.IC, g.x_stride = x.data_ptr(), M, ic, ic
                     g.group_size, g.kernel, g.split_k = 128, args.kernel, args.split_k
+                    g.reserved = args.debug
                     r_buf = torch.zeros(M, rank, dtype=torch.float16, device=dev)
                     if mode == "corr":
                         g.rank, g.r_mode, g.R, g.R_stride, g.r_buf = rank, K.R_COMPUTE, R.data_ptr(), ic, r_buf.data_ptr()
