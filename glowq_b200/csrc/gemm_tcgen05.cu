@@ -46,22 +46,25 @@ constexpr int kPBytes = BN * (BK / 8) * 4;  // 4 KB packed per 128 output column
 // per 256 output columns) and needs all 512 TMEM columns for its four accumulators, so the correction must
 // accumulate in place (alpha == 1); NN = 1 keeps a separate correction accumulator for any alpha.
 template <int NN> struct Cfg {
-  static constexpr int kMaxStages = 8;
-  // dequant (then epilogue) warps: one thread per half-row (32 columns) of the step's 128 NN-row packed tile.  The
-  // dequantisation is the slower side of the pipeline at large M, and it is latency-bound: more warps, not wider ones.
+  static constexpr int kMaxStages = 8, kMaxPStages = 16;
+  // dequant (then epilogue) warps: one thread per half-row (32 columns) of the step's 128 NN-row packed tile.
   static constexpr int kDequantWarps = 8 * NN;
-  static constexpr int kThreads = 64 + 32 * kDequantWarps;
+  static constexpr int kCtrlWarps = 3;  // operand producer, MMA issuer, packed-weight producer
+  static constexpr int kThreads = 32 * (kCtrlWarps + kDequantWarps);
   // The dequant warps work in kPassGroups teams; team g converts the packed tiles of steps g, g + kPassGroups, ...
   // (each thread then covers kPassGroups half-rows of a step), so that the fixed latency of a pass - barrier wake-up,
   // shared-memory round trip, proxy fence - overlaps between consecutive steps instead of adding up.
   static constexpr int kPassGroups = GLOWQ_GEMM_PASS_GROUPS;
-  // A stage holds mt activation tiles, NN operand tiles and NN packed tiles; the ring is as deep as 227 KB allow
-  // (3 stages for the 256 x 256 tile, 4 for 128 x 256, 6 for 128 x 128): narrow launches are bound by the latency
-  // of the weight stream, which only depth hides.
-  static constexpr int stage_bytes(int mt) { return mt * kABytes + NN * (kBBytes + kPBytes); }
+  // An operand stage holds mt activation tiles and NN weight tiles (fp16, swizzled); a packed stage NN int4 tiles.
+  // The operand ring is as deep as 227 KB allow after the packed ring: 3 stages for the 256 x 256 tile, 4 for
+  // 128 x 256 and 256 x 128, 6 for 128 x 128.
+  static constexpr int stage_bytes(int mt) { return mt * kABytes + NN * kBBytes; }
+  static constexpr int kPStageBytes = NN * kPBytes;
+  static constexpr int kPStages = NN == 2 ? 4 : 8;
   static constexpr int kSmemMax = 227 * 1024 - 256;  // the kernel also has a few bytes of static shared memory
-  static int stages(int mt) { return std::min(kMaxStages, (kSmemMax - 2048) / stage_bytes(mt)); }
-  static int smem(int mt) { return 2048 + stages(mt) * stage_bytes(mt); }  // 1 KB alignment slack + 1 KB of barriers + ring
+  static int stages(int mt) { return std::min(kMaxStages, (kSmemMax - 2048 - kPStages * kPStageBytes) / stage_bytes(mt)); }
+  // 1 KB alignment slack + 1 KB of barriers + the rings
+  static int smem(int mt) { return 2048 + stages(mt) * stage_bytes(mt) + kPStages * kPStageBytes; }
 };
 constexpr uint32_t kGemmSpin = 1u << 18;
 constexpr uint32_t kTmemCols = 512;
@@ -78,13 +81,12 @@ struct GemmParams {
   uint32_t* status;
   int M, nk1, w4, out_fp32, n_members;
   int mt;  // 128-token accumulators per CTA actually used (1 or 2): 1 spreads a narrow product over more CTAs
-  int stages;  // ring depth for this mt
+  int stages, pstages;  // ring depths (operands, packed weights) for this mt
   // split-K (only the narrow r = X . R^T product uses it): gridDim.z CTAs share a tile's K steps, each writes its fp32
-  // partial tile to its own slot, and the last one to arrive adds the slots in order and stores the result
+  // partial tile to its own slot; slot_sum_kernel then adds the slots in slice order
   int ksplit;
   int debug;         // tuning experiments only (0 in production): 16 no copies after the first ring round, 32 no MMA, 64 no dequant
-  float* slots;      // [ksplit][tiles][NN * MT * 128 * 128]
-  uint32_t* kctr;    // [tiles] arrival counters, zero between launches
+  float* slots;      // [ksplit][tiles][NN * mt * 128 * 128]
   GemmMember mem[kMaxMembers];
 };
 struct alignas(64) GemmMaps {
@@ -188,17 +190,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 template <int NN>
 __global__ void __launch_bounds__(Cfg<NN>::kThreads, 1)
 gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ GemmMaps tm) {
-  const int kStagesG = p.stages;
-  const uint32_t kBOff = p.mt * kABytes;            // B tiles inside a stage
-  const uint32_t kPOff = kBOff + NN * kBBytes;      // packed tiles inside a stage
-  const uint32_t kStageG = kPOff + NN * kPBytes;
+  const int kStagesG = p.stages, kPStagesG = p.pstages;
+  const uint32_t kBOff = p.mt * kABytes;              // B tiles inside an operand stage
+  const uint32_t kStageG = kBOff + NN * kBBytes;      // operand stage: mt activation tiles + NN weight tiles
+  constexpr uint32_t kPStage = NN * kPBytes;          // packed stage
   extern __shared__ unsigned char smem[];
   __shared__ int s_abort;
   __shared__ uint32_t s_tmem_base;
   const uint32_t smem0 = (sm_u32(smem) + 1023u) & ~1023u;  // swizzled operand tiles want 1024-byte alignment
-  // barriers live in the first 1 KB: full[8], empty[8], bready[8], accum
-  const uint32_t full_b = smem0, empty_b = smem0 + 64, bready_b = smem0 + 128, accum_b = smem0 + 192;
+  // barriers live in the first 1 KB: full[8], empty[8], bready[8], pfull[16], pempty[16], accum
+  const uint32_t full_b = smem0, empty_b = smem0 + 64, bready_b = smem0 + 128, pfull_b = smem0 + 192,
+                 pempty_b = smem0 + 320, accum_b = smem0 + 448;
   const uint32_t ring = smem0 + 1024;
+  const uint32_t pring = ring + kStagesG * kStageG;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int mi = 0;
 #pragma unroll
@@ -211,6 +215,7 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   const int nk_all = (p.debug & 1024) ? (p.nk1 + mb.nk2) / 4 : p.nk1 + mb.nk2;
   const int it0 = p.ksplit > 1 ? static_cast<int>(static_cast<long long>(nk_all) * blockIdx.z / p.ksplit) : 0;
   const int nk = p.ksplit > 1 ? static_cast<int>(static_cast<long long>(nk_all) * (blockIdx.z + 1) / p.ksplit) : nk_all;
+  const int nk_packed = p.w4 ? min(nk, p.nk1) : it0;  // steps [it0, nk_packed) dequantise a packed tile
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -218,6 +223,10 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       g_mbar_init(full_b + 8 * i, 1);
       g_mbar_init(empty_b + 8 * i, 1);
       g_mbar_init(bready_b + 8 * i, Cfg<NN>::kDequantWarps / Cfg<NN>::kPassGroups);
+    }
+    for (int i = 0; i < kPStagesG; ++i) {
+      g_mbar_init(pfull_b + 8 * i, 1);
+      g_mbar_init(pempty_b + 8 * i, Cfg<NN>::kDequantWarps / Cfg<NN>::kPassGroups);
     }
     g_mbar_init(accum_b, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -238,33 +247,43 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   auto tr = [&](int role, int ev, int step) {
     if (tracing && step < 256) trace[(role * 3 + ev) * 256 + step] = clock64();
   };
-  const int spin1 = (p.debug & 128) ? 4096 : 0, spin2 = (p.debug & 256) ? 256 : 0;
+  // after a failed wait: give the copies of the last `depth` issues a bounded time to land
+  auto drain = [&](uint32_t bars, int depth, int issued) {
+    for (int j = (issued > depth ? issued - depth : 0); j < issued; ++j) {
+      uint32_t spins = 0, done = 0;
+      while (!done && ++spins < kGemmSpin)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(bars + 8 * (j % depth)), "r"((j / depth) & 1)
+            : "memory");
+    }
+  };
 
   if (warp == 0) {
-    // ================================================================ TMA producer (one thread: a wait that the
-    // whole warp executes costs 32 serialised barrier operations)
+    // ================================================================ operand producer (one thread: a wait that
+    // the whole warp executes costs 32 serialised barrier operations): activation tiles, and the B tile of the
+    // steps that need no dequantisation
     if (lane == 0) {
       uint32_t st = 0, ph = 0;
       int issued = 0;
       bool ok = true;
-      for (int it = it0; it < nk && ok; ++it) {
+      for (int it = it0; it < nk; ++it) {
         tr(0, 0, it - it0);
-        if (!(ok = g_mbar_wait(empty_b + 8 * st, ph ^ 1, abort_flag, p.status, spin1))) break;
+        if (!(ok = g_mbar_wait(empty_b + 8 * st, ph ^ 1, abort_flag, p.status))) break;
         tr(0, 1, it - it0);
         const uint32_t sbase = ring + st * kStageG, bar = full_b + 8 * st;
         const bool phase1 = it < p.nk1;
         const int kk = phase1 ? it : it - p.nk1;
-        const bool packed = phase1 && p.w4;
+        const bool packed = it < nk_packed;
         if ((p.debug & 16) && it - it0 >= kStagesG) {
           g_mbar_arrive(bar);
         } else {
-          g_mbar_expect_tx(bar, n_mt * kABytes + NN * (packed ? kPBytes : kBBytes));
+          g_mbar_expect_tx(bar, n_mt * kABytes + (packed ? 0 : NN * kBBytes));
           const CUtensorMap* ta = phase1 ? &tm.a1 : &tm.a2;
           g_tma_2d(sbase, ta, kk * BK, m0, bar);
           if (n_mt == 2) g_tma_2d(sbase + kABytes, ta, kk * BK, m0 + BM, bar);
-          if (packed)  // one box of 128 NN rows x 32 B
-            g_tma_2d(sbase + kPOff, &tm.b1[mi], kk * (BK / 8), n0, bar);
-          else  // one box of 128 NN rows x 128 B, swizzled: NN consecutive 16 KB operand tiles
+          if (!packed)  // one box of 128 NN rows x 128 B, swizzled: NN consecutive 16 KB operand tiles
             g_tma_2d(sbase + kBOff, phase1 ? &tm.b1[mi] : &tm.b2[mi], kk * BK, n0, bar);
         }
         ++issued;
@@ -273,22 +292,37 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           ph ^= 1;
         }
       }
-      if (!ok) {  // wait (bounded) for copies that are still in flight
-        for (int j = (issued > kStagesG ? issued - kStagesG : 0); j < issued; ++j) {
-          uint32_t spins = 0, done = 0;
-          while (!done && ++spins < kGemmSpin)
-            asm volatile(
-                "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                : "=r"(done)
-                : "r"(full_b + 8 * (j % kStagesG)), "r"((j / kStagesG) & 1)
-                : "memory");
+      if (!ok) drain(full_b, kStagesG, issued);
+    }
+    __syncwarp();
+  } else if (warp == 2) {
+    // ================================================================ packed-weight producer (one thread).  The
+    // packed tiles are small, so their ring runs many steps ahead of the operand ring: the DRAM latency of the
+    // weight stream is then off the path stage-free -> tile-dequantised -> MMA.
+    if (lane == 0) {
+      uint32_t sp = 0, pph = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int it = it0; it < nk_packed; ++it) {
+        if (!(ok = g_mbar_wait(pempty_b + 8 * sp, pph ^ 1, abort_flag, p.status))) break;
+        const uint32_t bar = pfull_b + 8 * sp;
+        if ((p.debug & 16) && it - it0 >= kPStagesG) {
+          g_mbar_arrive(bar);
+        } else {
+          g_mbar_expect_tx(bar, kPStage);
+          g_tma_2d(pring + sp * kPStage, &tm.b1[mi], it * (BK / 8), n0, bar);  // one box of 128 NN rows x 32 B
+        }
+        ++issued;
+        if (++sp == static_cast<uint32_t>(kPStagesG)) {
+          sp = 0;
+          pph ^= 1;
         }
       }
+      if (!ok) drain(pfull_b, kPStagesG, issued);
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ================================================================ MMA issuer (one thread).  The dequant warps
-    // wait for the stage's copies before they arrive on `bready`, so that barrier alone says that A and B are in place.
+    // ================================================================ MMA issuer (one thread)
     if (lane == 0) {
       // A single thread runs this loop, so every instruction in it is latency on the critical path: descriptors are
       // one 32-bit add each (the address field, in 16-byte units, never carries out of the low word).
@@ -301,7 +335,8 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       const uint32_t stage16 = kStageG >> 4, boff16 = kBOff >> 4;
       const bool skip_mma = (p.debug & 32) != 0;
       for (int it = it0; it < nk; ++it) {
-        if (ok && !g_mbar_try_once(bready_b + 8 * st, ph)) ok = g_mbar_wait(bready_b + 8 * st, ph, abort_flag, p.status, spin1);
+        if (ok && !g_mbar_try_once(bready_b + 8 * st, ph)) ok = g_mbar_wait(bready_b + 8 * st, ph, abort_flag, p.status);
+        if (ok && !g_mbar_try_once(full_b + 8 * st, ph)) ok = g_mbar_wait(full_b + 8 * st, ph, abort_flag, p.status);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok && !(skip_mma && it > it0)) {
           const bool phase2 = it >= p.nk1;
@@ -322,8 +357,7 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
             }
           }
         }
-        if (p.debug & 512) g_mbar_arrive(empty_b + 8 * st);
-        else umma_commit(empty_b + 8 * st);  // the stage is free once the MMAs above have read it
+        umma_commit(empty_b + 8 * st);  // the stage is free once the MMAs above have read it
         tr(1, 2, it - it0);
         desc_lo += stage16;
         if (++st == static_cast<uint32_t>(kStagesG)) {
@@ -337,11 +371,12 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     __syncwarp();
   } else {
     // ================================================================ dequant warps, then epilogue
-    // one thread per half-row (32 columns) of the step's 128 NN-row packed tile
+    // one thread per half-row (32 columns) of the step's 128 NN-row packed tile, kPassGroups such half-rows per pass
     constexpr int H = Cfg<NN>::kPassGroups;
     constexpr int kGroupThreads = Cfg<NN>::kDequantWarps * 32 / H;
-    const int dt = threadIdx.x - 64;
+    const int dt = threadIdx.x - 32 * Cfg<NN>::kCtrlWarps;
     const int pg = dt / kGroupThreads, lt = dt - pg * kGroupThreads;  // pass group, thread within it
+    const bool tr_warp = warp == Cfg<NN>::kCtrlWarps;
     int rloc[H], half[H];
     bool rvalid[H];
     uint32_t b_row[H], sw[H];
@@ -354,7 +389,7 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       b_row[h] = (static_cast<uint32_t>(rloc[h]) >> 3) * 1024 + (static_cast<uint32_t>(rloc[h]) & 7) * 128;
       sw[h] = static_cast<uint32_t>(rloc[h]) & 7;
     }
-    uint32_t st = pg, ph = 0;   // kPassGroups <= ring depth
+    uint32_t st = pg, ph = 0, sp = pg, pph = 0;   // kPassGroups <= ring depths
     bool ok = true;
     // scale / zero-point of a row: quantisation group G covers steps 2G and 2G+1; the pair for the next step this pass
     // group will handle is fetched one pass ahead, so that the global-load latency never sits between a stage
@@ -377,14 +412,15 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     }
     int cur_g = -1;
     for (int it = it0 + pg; it < nk; it += H) {
-      if (warp == 2) tr(2, 0, it - it0);
-      if (lane == 0) {  // one lane polls; the stage's copies must have landed before this warp reports the tile ready
-        ok = ok && g_mbar_wait(empty_b + 8 * st, ph ^ 1, abort_flag, p.status, spin2);
-        ok = ok && g_mbar_wait(full_b + 8 * st, ph, abort_flag, p.status, spin2);
+      const bool packed = it < nk_packed;
+      if (tr_warp) tr(2, 0, it - it0);
+      if (lane == 0) {  // one lane polls: the packed tile has landed, and the MMAs that read this B slot are done
+        if (packed) ok = ok && g_mbar_wait(pfull_b + 8 * sp, pph, abort_flag, p.status);
+        ok = ok && g_mbar_wait(empty_b + 8 * st, ph ^ 1, abort_flag, p.status);
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (warp == 2) tr(2, 1, it - it0);
-      if (it < p.nk1 && p.w4 && !(p.debug & 64)) {
+      if (tr_warp) tr(2, 1, it - it0);
+      if (packed) {
         if ((it >> 1) != cur_g) {  // first step of this pass group in quantisation group it/2
           cur_g = it >> 1;
 #pragma unroll
@@ -397,11 +433,11 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
 #pragma unroll
           for (int h = 0; h < H; ++h) fetch_sz(h, (it + H) >> 1, nx_s[h], nx_z[h]);
         }
-        if (ok) {
-          const uint32_t sbase = ring + st * kStageG;
+        if (ok && !(p.debug & 64)) {
+          const uint32_t sbase = ring + st * kStageG, psrc = pring + sp * kPStage;
 #pragma unroll
           for (int h = 0; h < H; ++h) {
-            const uint32_t pbase = sbase + kPOff + rloc[h] * 32 + half[h] * 16;
+            const uint32_t pbase = psrc + rloc[h] * 32 + half[h] * 16;
             uint32_t w[4];
             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(pbase));
             const uint32_t bbase = sbase + kBOff + b_row[h];  // row rloc of the NN stacked 128-row tiles
@@ -423,12 +459,22 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         }
       }
       __syncwarp();
-      if (lane == 0) g_mbar_arrive(bready_b + 8 * st);
-      if (warp == 2) tr(2, 2, it - it0);
+      if (lane == 0) {
+        g_mbar_arrive(bready_b + 8 * st);
+        if (packed) g_mbar_arrive(pempty_b + 8 * sp);
+      }
+      if (tr_warp) tr(2, 2, it - it0);
       st += H;
       if (st >= static_cast<uint32_t>(kStagesG)) {
         st -= kStagesG;
         ph ^= 1;
+      }
+      if (packed) {
+        sp += H;
+        if (sp >= static_cast<uint32_t>(kPStagesG)) {
+          sp -= kPStagesG;
+          pph ^= 1;
+        }
       }
     }
 
@@ -438,7 +484,7 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     const int q = warp & 3;                          // TMEM lane quadrant this warp may read
     constexpr int kWays = Cfg<NN>::kDequantWarps / 4;  // warps that share a lane quadrant split the tile's columns
     constexpr int kCbPer = (BN / 32) / kWays;
-    const int cb0 = ((warp - 2) >> 2) * kCbPer;
+    const int cb0 = ((warp - Cfg<NN>::kCtrlWarps) >> 2) * kCbPer;
     // bias, conversion and store of 32 consecutive columns c0.. of token tok
     auto emit = [&](float (&v)[32], int tok, int c0) {
       if (mb.bias) {
@@ -511,42 +557,6 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         }
       }
     }
-    if (p.ksplit > 1) {  // the last CTA of the tile to get here adds the slots (in slice order: deterministic)
-      __shared__ int s_last;
-      __threadfence();
-      asm volatile("bar.sync 1, %0;" ::"n"(Cfg<NN>::kDequantWarps * 32) : "memory");
-      if (threadIdx.x == 64) s_last = (atomicAdd(p.kctr + tile_lin, 1u) == static_cast<uint32_t>(p.ksplit - 1));
-      asm volatile("bar.sync 1, %0;" ::"n"(Cfg<NN>::kDequantWarps * 32) : "memory");
-      if (s_last) {
-        __threadfence();
-        for (int at = 0; at < NN * MT; ++at) {
-          const int nn = at / MT, mt = at - nn * MT;
-          if (mt >= n_mt || nn >= n_nt) continue;
-          const int tok = m0 + mt * BM + q * 32 + lane;
-          for (int cb = cb0; cb < cb0 + kCbPer; ++cb) {
-            const int c0 = n0 + nn * BN + cb * 32;
-            if (!(ok && tok < p.M)) continue;
-            float v[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = 0.f;
-            for (int z = 0; z < p.ksplit; ++z) {
-              const float* sl = p.slots + (static_cast<size_t>(z) * n_tiles_all + tile_lin) * kSlotFloats +
-                                static_cast<size_t>(at) * (BM * BN) + (q * 32 + lane) * BN + cb * 32;
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                const float4 t = __ldcg(reinterpret_cast<const float4*>(sl + j));
-                v[j] += t.x;
-                v[j + 1] += t.y;
-                v[j + 2] += t.z;
-                v[j + 3] += t.w;
-              }
-            }
-            emit(v, tok, c0);
-          }
-        }
-        if (threadIdx.x == 64) p.kctr[tile_lin] = 0;  // ready for the next launch
-      }
-    }
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -555,6 +565,30 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
+}
+
+// out[tok, col..col+3] = half(sum over slices of the 128 x 128 fp32 slot tiles), slices added in order.
+__global__ void slot_sum_kernel(const float* __restrict__ slots, __half* __restrict__ out, int M, int N, int out_stride,
+                                int ksplit, int tiles_x, int tiles_all) {
+  const int quads = N >> 2;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= M * quads) return;
+  const int tok = idx / quads, col = (idx - tok * quads) << 2;
+  const size_t tile = static_cast<size_t>(tok / BM) * tiles_x + col / BN;
+  const size_t in_tile = static_cast<size_t>(tok % BM) * BN + (col % BN);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int z = 0; z < ksplit; ++z) {
+    const float4 t = __ldcg(reinterpret_cast<const float4*>(slots + (static_cast<size_t>(z) * tiles_all + tile) * (BM * BN) + in_tile));
+    acc.x += t.x;
+    acc.y += t.y;
+    acc.z += t.z;
+    acc.w += t.w;
+  }
+  __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
+  uint2 pk;
+  pk.x = *reinterpret_cast<uint32_t*>(&lo);
+  pk.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(out + static_cast<size_t>(tok) * out_stride + col) = pk;
 }
 
 inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -575,6 +609,7 @@ cudaError_t launch_gemm_nn(const GemmParams& p, const GemmMaps& tm, cudaStream_t
   for (int i = 0; i < p.n_members; ++i) n_tiles = std::max(n_tiles, p.mem[i].tile_begin + cdiv(p.mem[i].OC, BN * NN));
   GemmParams q = p;
   q.stages = Cfg<NN>::stages(p.mt);
+  q.pstages = Cfg<NN>::kPStages;
   if (q.ksplit < 1) q.ksplit = 1;
   dim3 grid(n_tiles, cdiv(p.M, BM * p.mt), q.ksplit);
   gemm_w4a16_kernel<NN><<<grid, Cfg<NN>::kThreads, Cfg<NN>::smem(p.mt), stream>>>(q, tm);
@@ -604,12 +639,10 @@ bool gemm_supported(const glowq_w4a16_group_t& g) {
 
 // K slices of the r = X . R^T product (a [M, rank] output is a handful of tiles: without slicing a few CTAs would
 // walk all of K while the rest of the GPU idles).  Device-independent so that the workspace size is, too.
-constexpr int kKctrWord = 8;                                   // header words [8, 64) hold the tiles' arrival counters
-constexpr int kKctrTiles = WS_HEADER_WORDS - kKctrWord;
 constexpr size_t kRSlotBytes = static_cast<size_t>(BM) * BN * 4;   // slot of an NN = 1, mt = 1 tile
 inline int r_ksplit(int M, int IC, int rank) {
   const int tiles = cdiv(rank, BN) * cdiv(M, BM), nk = cdiv(IC, BK);
-  if (tiles > kKctrTiles) return 1;
+  if (tiles > 64) return 1;
   return std::max(1, std::min({16, nk / 4, 128 / tiles}));
 }
 
@@ -672,13 +705,18 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
       slot_off = kWsHeaderBytes;
     }
     p.slots = reinterpret_cast<float*>(static_cast<unsigned char*>(g.workspace) + slot_off);
-    p.kctr = static_cast<uint32_t*>(g.workspace) + kKctrWord;
     p.mem[0].out = g.r_buf;
     p.mem[0].OC = g.rank;
     p.mem[0].out_stride = g.rank;
     p.mem[0].alpha = 1.f;
     p.mem[0].out_vec_ok = 1;  // rank % 8 == 0 and r_buf aligned
     cudaError_t e = launch_gemm(p, tm, 1, stream);
+    if (e == cudaSuccess && p.ksplit > 1) {
+      const int tiles_x = cdiv(g.rank, BN), tiles_all = tiles_x * cdiv(g.M, BM), n = g.M * (g.rank >> 2);
+      slot_sum_kernel<<<cdiv(n, 256), 256, 0, stream>>>(p.slots, static_cast<__half*>(g.r_buf), g.M, g.rank, g.rank, p.ksplit,
+                                                        tiles_x, tiles_all);
+      e = cudaGetLastError();
+    }
     if (e != cudaSuccess) {
       *cuda_err = e;
       return GLOWQ_ERR_CUDA;
