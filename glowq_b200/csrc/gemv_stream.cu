@@ -77,6 +77,15 @@ struct Ctx {
   int mode;
 };
 
+// Tuning aid (debug & 16, needs a workspace of at least 40 MB): event e of CTA b -> %globaltimer at workspace + 32 MB.
+__device__ __forceinline__ void trace_event(const GemvParams& p, int e) {
+  if (p.debug & 16) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(p.ws_head) + (32u << 20))[blockIdx.x * 16 + e] = t;
+  }
+}
+
 // ---------------------------------------------------------------- activations
 // Stage x[0:M, g0*128 : (g0+ng)*128) into shared memory in MMA B-fragment order: for token m and group gl,
 // 16-byte chunk (i*4 + t) holds the columns 32t+8i+{0,4,1,5,2,6,3,7} of that group, the ones at odd positions of
@@ -369,6 +378,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   // Programmatic dependent launch: let the next kernel of the stream start its own prologue (barrier set-up, weight
   // and metadata copies - nothing that depends on this kernel) as soon as every CTA of this grid is resident.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (threadIdx.x == 0) trace_event(p, 0);
   if (threadIdx.x == 0) {
     s_abort = 0;
     for (int i = 0; i < kMaxStages; ++i) {
@@ -384,6 +394,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  if (threadIdx.x == 0) trace_event(p, 1);
   Ctx cx{&s_abort, p.ws_head + WS_STATUS, p.debug};
   const uint32_t full_u32 = smem_u32(full_bar), empty_u32 = smem_u32(empty_bar);
   const uint32_t mfull_u32 = smem_u32(meta_full), mempty_u32 = smem_u32(meta_empty);
@@ -557,6 +568,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
         }
       }
     }
+    if (lane == 0) trace_event(p, 9);
     asm volatile("cp.async.wait_all;" ::: "memory");  // nothing of this warp is in flight when the CTA retires
   } else {
     // ================================================================ consumer warps
@@ -573,9 +585,12 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       for (int u = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x); u < p.n_r_units; u += gridDim.x)
         r_unit<NT>(p, u, red, fin, dep_wait_pending);
     }
+    if (threadIdx.x == 0 && r_only) trace_event(p, 6);
     if (dep_wait_pending) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 0) trace_event(p, 2);
     if (!r_only || deal_all) stage_x(p, g0, ng, xs, xsum, 8 * NT);
     consumer_sync();  // publishes xs / xsum
+    if (threadIdx.x == 0) trace_event(p, 3);
 
     // per-lane constant shared addresses: weight quad (warp's group, lane's 16 B, lane's row), x chunk, x sums
     const uint32_t ring_lane = smem_u32(ring) + warp * 64 + t * 16 + g * kRowPitch;
@@ -610,6 +625,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       //   sum_k (n_k - z) x_k = sum_k n_k x_k - z * sum_k x_k,   with sum_k x_k staged per (group, token).
       for (int c = 0; c < n_chunks; ++c) {
         ok = ok && mbar_wait_u32(full_u32 + st * 8, ph, cx);
+        if (threadIdx.x == 0 && k == 0 && c == 0) trace_event(p, 4);
         const int gl = c * kChunkGroups + warp;
         if (ok && gl < ng && !(p.debug & 1)) {
           const uint32_t wbase = ring_lane + st * kStageBytes;
@@ -669,11 +685,13 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
         }
       }
 
+      if (threadIdx.x == 0 && k == 0) trace_event(p, 5);
       if (ti.corr) {
         if (!r_ready) {  // r comes from R units of this launch: bounded wait on the release counter
           if (lane == 0) wait_r_done(p, &s_abort);
           __syncwarp();
           r_ready = true;
+          if (threadIdx.x == 0) trace_event(p, 7);
         }
         float al[NB][4];
 #pragma unroll
@@ -745,6 +763,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       else
         asm volatile("bar.arrive 3, %0;" ::"n"(kConsumerThreads + 32) : "memory");
       if ((rbuf ^= 1) == 0) rph ^= 1;
+      if (threadIdx.x == 0 && k == 0) trace_event(p, 8);
     }
 
     // The CTA that ran R unit 0 leaves r in r_buf (fp16) for later launches of the group that load it.
@@ -760,6 +779,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   }
 
   __syncthreads();
+  if (threadIdx.x == 0) trace_event(p, 10);
   if (p.r_mode == 1 && threadIdx.x == 0) {
     const uint32_t old = atomicAdd(p.ws_head + WS_EXIT, 1u);
     if (old == gridDim.x - 1) {  // last CTA out re-arms the counters for the next launch
@@ -872,9 +892,10 @@ static cudaError_t launch_nt(const GemvParams& p, const TensorMaps& tm, int grid
 }
 
 cudaError_t launch_gemv_stream(const GemvParams& p, const TensorMaps& tm, int NT, int grid, cudaStream_t stream) {
-  if (NT <= 1) return launch_nt<1>(p, tm, grid, stream);
-  if (NT <= 2) return launch_nt<2>(p, tm, grid, stream);
-  return launch_nt<4>(p, tm, grid, stream);
+  // Launches carry at most 8 tokens (one token block): wider instantiations measured 3-13x slower per token than
+  // repeated 8-token launches, so the host splits larger batches or takes the tensor-core GEMM.
+  if (NT != 1) return cudaErrorInvalidValue;
+  return launch_nt<1>(p, tm, grid, stream);
 }
 
 cudaError_t launch_generic_r(const __half* x, const __half* R, __half* r_buf, float* r32, int r_mode, int M, int IC,
