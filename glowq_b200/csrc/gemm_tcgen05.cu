@@ -2,20 +2,25 @@
 //
 //   Y[M, OC] = X[M, IC] . dequant(Q)^T  +  alpha * r[M, rank] . L[OC, rank]^T  (+ bias),     r = X . R^T
 //
-// One CTA computes a 256-token x 256-column block of Y as four 128x128 fp32 accumulators in tensor memory (256 x 128
-// with a separate correction accumulator when alpha != 1).  K runs through a shared-memory ring in steps of 64:
-//   warp 0      TMA producer: the two 128x64 activation tiles (128-byte swizzle) and the 128 x 32 B packed
-//               int4 tile of the step; in the correction phase the r tiles and the L tile (fp16, swizzled, no
-//               dequantisation) - the correction is simply more K steps of the same pipeline.
-//   warps 2-9   dequantise: two threads per row turn the packed tile's row into 64 fp16 values half_rn((code - zero) *
-//               scale) - the same exact-integer unpack + one HMUL2 as the stand-alone dequant kernel, so the
-//               shared-memory tile is bit-identical to the reference's dequantised weight - and stores them as
-//               row i of the K-major, 128-byte-swizzled B tile; afterwards they are the epilogue (TMEM -> registers
-//               -> bias / alpha -> global).
-//   warp 1      allocates tensor memory and issues tcgen05.mma (one elected lane): 2 accumulators x 4 k16 slices
-//               per step, then tcgen05.commit to release the stage.
+// One CTA computes a block of Y (256 tokens x 256 columns as four 128 x 128 fp32 accumulators in tensor memory, or
+// 128-token / 128-column variants; 256 x 128 with a separate correction accumulator when alpha != 1); a CTA PAIR
+// (cluster of two, cta_group::2 MMAs) computes 256 tokens x 512 columns.  K runs in steps of 64 through two
+// shared-memory rings: operand stages (activation tiles + fp16 weight tiles, 128-byte swizzle) and, many steps ahead
+// of them, small packed stages (the int4 tiles as they lie in HBM).
+//   warp 0      operand producer (one thread): TMA of the activation tiles; in the correction phase also the L tile
+//               (fp16, swizzled, no dequantisation) - the correction is simply more K steps of the same pipeline.
+//   warp 2      packed-weight producer (one thread): TMA of the 128 NN x 32 B int4 tile of each step.
+//   warps 3..   dequantise, in kPassGroups teams that take alternate steps: a thread turns half-rows of the packed tile
+//               into 32 fp16 values half_rn((code - zero) * scale) - the same exact-integer unpack + one HMUL2 as the
+//               stand-alone dequant kernel, so the shared-memory tile is bit-identical to the reference's dequantised
+//               weight - and stores them into the K-major, 128-byte-swizzled B tile of the operand stage; afterwards
+//               these warps are the epilogue (TMEM -> registers -> bias / alpha -> global).
+//   warp 1      allocates tensor memory and issues tcgen05.mma from one thread (N = 256 per instruction where two
+//               weight tiles are stacked), then tcgen05.commit to release the stage.  In a pair only CTA 0 issues;
+//               the peer's warp 1 relays "my operand copies have landed" to CTA 0's barrier.
 // The dequantised weight never goes to HBM (the reference writes and re-reads a full fp16 copy per call).
-// The same kernel with an fp16 B operand by TMA (no dequant warps' work) computes r = X . R^T.
+// The same kernel with an fp16 B operand by TMA (no dequant work) computes r = X . R^T, K-sliced over gridDim.z
+// into fp32 slots that slot_sum_kernel adds up in slice order.
 // Every mbarrier wait is bounded; on expiry a status word is set and the CTA drains and frees its tensor memory.
 #include <algorithm>
 #include <cstdlib>
@@ -34,6 +39,9 @@ namespace {
 
 #ifndef GLOWQ_GEMM_PASS_GROUPS
 #define GLOWQ_GEMM_PASS_GROUPS 2
+#endif
+#ifndef GLOWQ_GEMM_PAIR_PASS_GROUPS
+#define GLOWQ_GEMM_PAIR_PASS_GROUPS 2
 #endif
 constexpr int BM = 128;   // tokens per accumulator (MMA M)
 constexpr int MT = 2;     // accumulators per CTA
@@ -55,6 +63,7 @@ template <int NN> struct Cfg {
   // (each thread then covers kPassGroups half-rows of a step), so that the fixed latency of a pass - barrier wake-up,
   // shared-memory round trip, proxy fence - overlaps between consecutive steps instead of adding up.
   static constexpr int kPassGroups = GLOWQ_GEMM_PASS_GROUPS;
+  static constexpr int kPairPassGroups = GLOWQ_GEMM_PAIR_PASS_GROUPS;  // CTA pairs (4 operand and 4 packed stages)
   // An operand stage holds mt activation tiles and NN weight tiles (fp16, swizzled); a packed stage NN int4 tiles.
   // The operand ring is as deep as 227 KB allow after the packed ring: 3 stages for the 256 x 256 tile, 4 for
   // 128 x 256 and 256 x 128, 6 for 128 x 128.
@@ -130,6 +139,25 @@ __device__ __forceinline__ bool g_mbar_wait(uint32_t a, uint32_t parity, volatil
     }
   }
 }
+// the same with cluster-scope acquire: the arrivals come from the peer CTA as well
+__device__ __forceinline__ bool g_mbar_wait_cluster(uint32_t a, uint32_t parity, volatile int* abort_flag, uint32_t* status) {
+  uint32_t spins = 0;
+  for (;;) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(a), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((++spins & 63u) == 0 && *abort_flag) return false;
+    if (spins > kGemmSpin) {
+      *abort_flag = 1;
+      atomicExch(status, 3u);
+      return false;
+    }
+  }
+}
 __device__ __forceinline__ void g_tma_2d(uint32_t dst, const CUtensorMap* tmap, int x, int y, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
@@ -173,6 +201,37 @@ __device__ __forceinline__ bool g_mbar_try_once(uint32_t a, uint32_t parity) {
                : "memory");
   return ok != 0;
 }
+// ---- CTA-pair (cta_group::2) forms: one MMA spans two SMs (256 tokens), each CTA holding its 128 tokens of A and
+// half of the B rows; barriers of the peer CTA are reached through shared::cluster addresses.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {  // shared::cta -> shared::cluster of `rank`
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void g_mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void umma2_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+  // instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, M = 256 over the CTA pair, N columns
+  constexpr uint32_t kIdesc = (1u << 4) | ((static_cast<uint32_t>(N) >> 3) << 17) | ((256u >> 4) << 24);
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma2_commit(uint32_t cluster_bar) {  // arrives once all MMAs issued so far are done
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -187,9 +246,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr));
 }
 
-template <int NN>
+// PAIR: launched as clusters of two CTAs along x (NN = 2, mt = 1).  The pair computes 256 tokens x 512 columns: CTA r
+// holds tokens [128 r, 128 r + 128) and dequantises weight rows [256 r, 256 r + 256) of the tile, i.e. half of the B
+// rows of each of the two N = 256 MMAs per K slice - per flop, half the dequantisation and two thirds of the
+// shared-memory traffic of the single-CTA 256 x 256 tile.  CTA 0 issues the MMAs; its `bready` barriers count the
+// dequant warps of both CTAs, and its commits release the stages of both.
+template <int NN, bool PAIR>
 __global__ void __launch_bounds__(Cfg<NN>::kThreads, 1)
 gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ GemmMaps tm) {
+  static_assert(!PAIR || NN == 2, "the CTA pair works on two 128-row weight tiles per CTA");
+  constexpr int kPG = PAIR ? Cfg<NN>::kPairPassGroups : Cfg<NN>::kPassGroups;
   const int kStagesG = p.stages, kPStagesG = p.pstages;
   const uint32_t kBOff = p.mt * kABytes;              // B tiles inside an operand stage
   const uint32_t kStageG = kBOff + NN * kBBytes;      // operand stage: mt activation tiles + NN weight tiles
@@ -204,14 +270,18 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   const uint32_t ring = smem0 + 1024;
   const uint32_t pring = ring + kStagesG * kStageG;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t crank = PAIR ? cluster_ctarank() : 0u;   // 0: the CTA that issues the MMAs
+  const int bx = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);  // column tile index
   int mi = 0;
 #pragma unroll
   for (int i = 1; i < kMaxMembers; ++i)
-    if (i < p.n_members && static_cast<int>(blockIdx.x) >= p.mem[i].tile_begin) mi = i;
+    if (i < p.n_members && bx >= p.mem[i].tile_begin) mi = i;
   const GemmMember& mb = p.mem[mi];
-  const int n0 = (static_cast<int>(blockIdx.x) - mb.tile_begin) * (BN * NN), m0 = blockIdx.y * (BM * p.mt);
-  const int n_mt = (p.mt == 2 && m0 + BM < p.M) ? 2 : 1;
-  const int n_nt = (NN == 2 && n0 + BN < mb.OC) ? 2 : 1;
+  // n0: first weight row this CTA dequantises; m0: its first token
+  const int n0 = PAIR ? (bx - mb.tile_begin) * (2 * BN * NN) + static_cast<int>(crank) * (BN * NN) : (bx - mb.tile_begin) * (BN * NN);
+  const int m0 = PAIR ? blockIdx.y * (2 * BM) + static_cast<int>(crank) * BM : blockIdx.y * (BM * p.mt);
+  const int n_mt = (!PAIR && p.mt == 2 && m0 + BM < p.M) ? 2 : 1;
+  const int n_nt = PAIR ? 2 : ((NN == 2 && n0 + BN < mb.OC) ? 2 : 1);
   const int nk_all = (p.debug & 1024) ? (p.nk1 + mb.nk2) / 4 : p.nk1 + mb.nk2;
   const int it0 = p.ksplit > 1 ? static_cast<int>(static_cast<long long>(nk_all) * blockIdx.z / p.ksplit) : 0;
   const int nk = p.ksplit > 1 ? static_cast<int>(static_cast<long long>(nk_all) * (blockIdx.z + 1) / p.ksplit) : nk_all;
@@ -222,28 +292,36 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     for (int i = 0; i < kStagesG; ++i) {
       g_mbar_init(full_b + 8 * i, 1);
       g_mbar_init(empty_b + 8 * i, 1);
-      g_mbar_init(bready_b + 8 * i, Cfg<NN>::kDequantWarps / Cfg<NN>::kPassGroups);
+      // pair: the dequant warps of both CTAs, plus the peer's relay thread (its operand copies have landed)
+      g_mbar_init(bready_b + 8 * i, PAIR ? 2 * Cfg<NN>::kDequantWarps / kPG + 1 : Cfg<NN>::kDequantWarps / kPG);
     }
     for (int i = 0; i < kPStagesG; ++i) {
       g_mbar_init(pfull_b + 8 * i, 1);
-      g_mbar_init(pempty_b + 8 * i, Cfg<NN>::kDequantWarps / Cfg<NN>::kPassGroups);
+      g_mbar_init(pempty_b + 8 * i, Cfg<NN>::kDequantWarps / kPG);
     }
     g_mbar_init(accum_b, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sm_u32(&s_tmem_base)), "r"(kTmemCols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {  // warp 1 of both CTAs
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sm_u32(&s_tmem_base)), "r"(kTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sm_u32(&s_tmem_base)), "r"(kTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = s_tmem_base;
   volatile int* abort_flag = &s_abort;
   // debug & 2048: CTA 0 records clock64() per role / event / step at workspace + 4096 (tuning only)
   unsigned long long* trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(p.status) - WS_STATUS * 4 + 4096);
-  const bool tracing = (p.debug & 2048) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
+  const bool tracing = (p.debug & 2048) && blockIdx.x == ((p.debug >> 12) & 1) && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
   auto tr = [&](int role, int ev, int step) {
     if (tracing && step < 256) trace[(role * 3 + ev) * 256 + step] = clock64();
   };
@@ -322,8 +400,8 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ================================================================ MMA issuer (one thread)
-    if (lane == 0) {
+    // ================================================================ MMA issuer (one thread; in a pair, of CTA 0)
+    if (lane == 0 && crank == 0) {
       // A single thread runs this loop, so every instruction in it is latency on the critical path: descriptors are
       // one 32-bit add each (the address field, in 16-byte units, never carries out of the low word).
       uint32_t st = 0, ph = 0;
@@ -334,14 +412,34 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       const uint32_t desc_lo0 = desc_lo;
       const uint32_t stage16 = kStageG >> 4, boff16 = kBOff >> 4;
       const bool skip_mma = (p.debug & 32) != 0;
+      const uint32_t peer_empty = PAIR ? map_to_cta(empty_b, 1) : 0u, peer_accum = PAIR ? map_to_cta(accum_b, 1) : 0u;
       for (int it = it0; it < nk; ++it) {
-        if (ok && !g_mbar_try_once(bready_b + 8 * st, ph)) ok = g_mbar_wait(bready_b + 8 * st, ph, abort_flag, p.status);
-        if (ok && !g_mbar_try_once(full_b + 8 * st, ph)) ok = g_mbar_wait(full_b + 8 * st, ph, abort_flag, p.status);
+        if (PAIR) {  // `bready`: the dequant warps of both CTAs and the landing of the peer's operand copies
+          ok = ok && g_mbar_wait_cluster(bready_b + 8 * st, ph, abort_flag, p.status);
+          tr(1, 0, it - it0);
+          if (ok && !g_mbar_try_once(full_b + 8 * st, ph)) ok = g_mbar_wait(full_b + 8 * st, ph, abort_flag, p.status);
+          tr(1, 1, it - it0);
+        } else {
+          if (ok && !g_mbar_try_once(bready_b + 8 * st, ph)) ok = g_mbar_wait(bready_b + 8 * st, ph, abort_flag, p.status);
+          if (ok && !g_mbar_try_once(full_b + 8 * st, ph)) ok = g_mbar_wait(full_b + 8 * st, ph, abort_flag, p.status);
+        }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok && !(skip_mma && it > it0)) {
           const bool phase2 = it >= p.nk1;
           const uint32_t lr_off = (phase2 && mb.lr_separate) ? BN : 0;
           const bool first = phase2 ? (mb.lr_separate && it == p.nk1) : (it == it0);
+          if constexpr (PAIR) {
+            // accumulator n (TMEM columns 256 n ..): B rows 128 n .. of this CTA and of the peer, 256 columns in all
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+#pragma unroll
+              for (int k16 = 0; k16 < BK / 16; ++k16) {
+                const uint64_t ad = mk64(desc_lo + k16 * 2, desc_hi);
+                const uint64_t bd = mk64(desc_lo + boff16 + n * (kBBytes >> 4) + k16 * 2, desc_hi);
+                umma2_f16<2 * BN>(tmem_base + n * (2 * BN), ad, bd, (first && k16 == 0) ? 0u : 1u);
+              }
+            }
+          } else {
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
             if (mt < n_mt) {
@@ -356,8 +454,14 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
               }
             }
           }
+          }
         }
-        umma_commit(empty_b + 8 * st);  // the stage is free once the MMAs above have read it
+        if (PAIR) {  // the stage is free, in both CTAs, once the MMAs above have read it
+          umma2_commit(empty_b + 8 * st);
+          umma2_commit(peer_empty + 8 * st);
+        } else {
+          umma_commit(empty_b + 8 * st);  // the stage is free once the MMAs above have read it
+        }
         tr(1, 2, it - it0);
         desc_lo += stage16;
         if (++st == static_cast<uint32_t>(kStagesG)) {
@@ -366,13 +470,33 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           desc_lo = desc_lo0;
         }
       }
-      umma_commit(accum_b);
+      if (PAIR) {
+        umma2_commit(accum_b);
+        umma2_commit(peer_accum);
+      } else {
+        umma_commit(accum_b);
+      }
+    }
+    if (PAIR && lane == 0 && crank == 1) {
+      // relay: tell the MMA thread (CTA 0) when this CTA's operand copies of a stage have landed
+      const uint32_t bready0 = map_to_cta(bready_b, 0);
+      uint32_t st = 0, ph = 0;
+      bool ok = true;
+      for (int it = it0; it < nk; ++it) {
+        ok = ok && g_mbar_wait(full_b + 8 * st, ph, abort_flag, p.status);
+        g_mbar_arrive_cluster(bready0 + 8 * st);
+        tr(1, 1, it - it0);
+        if (++st == static_cast<uint32_t>(kStagesG)) {
+          st = 0;
+          ph ^= 1;
+        }
+      }
     }
     __syncwarp();
   } else {
     // ================================================================ dequant warps, then epilogue
     // one thread per half-row (32 columns) of the step's 128 NN-row packed tile, kPassGroups such half-rows per pass
-    constexpr int H = Cfg<NN>::kPassGroups;
+    constexpr int H = kPG;
     constexpr int kGroupThreads = Cfg<NN>::kDequantWarps * 32 / H;
     const int dt = threadIdx.x - 32 * Cfg<NN>::kCtrlWarps;
     const int pg = dt / kGroupThreads, lt = dt - pg * kGroupThreads;  // pass group, thread within it
@@ -390,6 +514,7 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       sw[h] = static_cast<uint32_t>(rloc[h]) & 7;
     }
     uint32_t st = pg, ph = 0, sp = pg, pph = 0;   // kPassGroups <= ring depths
+    const uint32_t bready0 = PAIR ? map_to_cta(bready_b, 0) : bready_b;
     bool ok = true;
     // scale / zero-point of a row: quantisation group G covers steps 2G and 2G+1; the pair for the next step this pass
     // group will handle is fetched one pass ahead, so that the global-load latency never sits between a stage
@@ -460,7 +585,11 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       }
       __syncwarp();
       if (lane == 0) {
-        g_mbar_arrive(bready_b + 8 * st);
+        if (PAIR && crank != 0) {
+          g_mbar_arrive_cluster(bready0 + 8 * st);
+        } else {
+          g_mbar_arrive(bready_b + 8 * st);
+        }
         if (packed) g_mbar_arrive(pempty_b + 8 * sp);
       }
       if (tr_warp) tr(2, 2, it - it0);
@@ -527,6 +656,28 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     const size_t kSlotFloats = static_cast<size_t>(NN) * p.mt * BM * BN;
     const size_t tile_lin = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
     const size_t n_tiles_all = static_cast<size_t>(gridDim.x) * gridDim.y;
+    if constexpr (PAIR) {
+      // two accumulators of 256 columns: column c of accumulator n is output column 128 n + c of this pair tile when
+      // c < 128 (rows CTA 0 dequantised), 256 + 128 n + (c - 128) otherwise (CTA 1's rows); 16 blocks of 32 columns
+      const int tile_n0 = (bx - mb.tile_begin) * (2 * BN * NN);
+      const int tok = m0 + q * 32 + lane;
+      constexpr int kUnits = 16 / kWays;
+      const int u0 = ((warp - Cfg<NN>::kCtrlWarps) >> 2) * kUnits;
+      for (int u = u0; u < u0 + kUnits; ++u) {
+        const int n = u >> 3, cb = u & 7;
+        uint32_t acc[32];
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + n * (2 * BN) + cb * 32, acc);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int c = cb * 32;
+        const int c0 = tile_n0 + (c < BN ? n * BN + c : 2 * BN + n * BN + (c - BN));
+        if (ok && tok < p.M && c0 < mb.OC) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]);
+          emit(v, tok, c0);
+        }
+      }
+    } else {
     for (int at = 0; at < NN * MT; ++at) {
       const int nn = at / MT, mt = at - nn * MT;
       if (mt >= n_mt || nn >= n_nt) continue;
@@ -557,13 +708,18 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         }
       }
     }
+    }
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // neither CTA retires while the other's MMAs or arrivals may still touch it
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    if (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -594,31 +750,48 @@ __global__ void slot_sum_kernel(const float* __restrict__ slots, __half* __restr
 inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int cdiv(int a, int b) { return (a + b - 1) / b; }
 
-template <int NN>
+template <int NN, bool PAIR>
 cudaError_t launch_gemm_nn(const GemmParams& p, const GemmMaps& tm, cudaStream_t stream) {
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_kernel<NN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_kernel<NN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          std::max(Cfg<NN>::smem(1), Cfg<NN>::smem(2)));
     if (e != cudaSuccess) return e;
     attr_done[dev] = true;
   }
+  const int cols_per_tile = BN * NN * (PAIR ? 2 : 1);
   int n_tiles = 0;
-  for (int i = 0; i < p.n_members; ++i) n_tiles = std::max(n_tiles, p.mem[i].tile_begin + cdiv(p.mem[i].OC, BN * NN));
+  for (int i = 0; i < p.n_members; ++i) n_tiles = std::max(n_tiles, p.mem[i].tile_begin + cdiv(p.mem[i].OC, cols_per_tile));
   GemmParams q = p;
   q.stages = Cfg<NN>::stages(p.mt);
   q.pstages = Cfg<NN>::kPStages;
   if (q.ksplit < 1) q.ksplit = 1;
-  dim3 grid(n_tiles, cdiv(p.M, BM * p.mt), q.ksplit);
-  gemm_w4a16_kernel<NN><<<grid, Cfg<NN>::kThreads, Cfg<NN>::smem(p.mt), stream>>>(q, tm);
-  return cudaGetLastError();
+  if (!PAIR) {
+    dim3 grid(n_tiles, cdiv(p.M, BM * p.mt), q.ksplit);
+    gemm_w4a16_kernel<NN, false><<<grid, Cfg<NN>::kThreads, Cfg<NN>::smem(p.mt), stream>>>(q, tm);
+    return cudaGetLastError();
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * n_tiles, cdiv(p.M, 2 * BM), 1);  // clusters of two CTAs along x
+  cfg.blockDim = dim3(Cfg<NN>::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg<NN>::smem(1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, gemm_w4a16_kernel<NN, PAIR>, q, tm);
 }
 
-// nn = 2 needs in-place accumulation of the correction (no separate accumulator columns left).
-cudaError_t launch_gemm(const GemmParams& p, const GemmMaps& tm, int nn, cudaStream_t stream) {
-  return nn == 2 ? launch_gemm_nn<2>(p, tm, stream) : launch_gemm_nn<1>(p, tm, stream);
+// nn = 2 needs in-place accumulation of the correction (no separate accumulator columns left); pair implies nn = 2.
+cudaError_t launch_gemm(const GemmParams& p, const GemmMaps& tm, int nn, bool pair, cudaStream_t stream) {
+  if (pair) return launch_gemm_nn<2, true>(p, tm, stream);
+  return nn == 2 ? launch_gemm_nn<2, false>(p, tm, stream) : launch_gemm_nn<1, false>(p, tm, stream);
 }
 
 }  // namespace
@@ -710,7 +883,7 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
     p.mem[0].out_stride = g.rank;
     p.mem[0].alpha = 1.f;
     p.mem[0].out_vec_ok = 1;  // rank % 8 == 0 and r_buf aligned
-    cudaError_t e = launch_gemm(p, tm, 1, stream);
+    cudaError_t e = launch_gemm(p, tm, 1, false, stream);
     if (e == cudaSuccess && p.ksplit > 1) {
       const int tiles_x = cdiv(g.rank, BN), tiles_all = tiles_x * cdiv(g.M, BM), n = g.M * (g.rank >> 2);
       slot_sum_kernel<<<cdiv(n, 256), 256, 0, stream>>>(p.slots, static_cast<__half*>(g.r_buf), g.M, g.rank, g.rank, p.ksplit,
@@ -737,30 +910,42 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
   // Tile shape: the 256 x 256 CTA tile has the best operand reuse, but a problem that fills the SMs badly in whole
   // waves is faster with narrower (nn = 1) or shorter (mt = 1) tiles.  A separate correction accumulator needs nn = 1.
   int nn = 1, mt = 2;
+  bool pair = false;
+  static const int env_pair = [] { const char* e = std::getenv("GLOWQ_GEMM_PAIR"); return e ? std::atoi(e) : -1; }();
   {
     int sms = 148, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     double best = -1.0;
+    auto consider = [&](int cnn, int cmt, bool cpair, long ctas, double reuse) {
+      const double wave_eff = static_cast<double>(ctas) / (static_cast<double>(cdiv(static_cast<int>(ctas), sms)) * sms);
+      if (wave_eff * reuse > best) {
+        best = wave_eff * reuse;
+        nn = cnn;
+        mt = cmt;
+        pair = cpair;
+      }
+    };
+    if (!any_separate && g.M > BM && env_pair == 1) {  // CTA pairs (measured no faster than one CTA per tile: opt-in): 256 tokens x 512 columns per pair
+      long tiles = 0;
+      for (int i = 0; i < g.n_members; ++i) tiles += cdiv(g.members[i].OC, 4 * BN);
+      consider(2, 1, true, 2 * tiles * cdiv(g.M, 2 * BM), 1.3);
+    }
     for (int cnn = any_separate ? 1 : 2; cnn >= 1; --cnn)
       for (int cmt = 2; cmt >= 1; --cmt) {
         long tiles = 0;
         for (int i = 0; i < g.n_members; ++i) tiles += cdiv(g.members[i].OC, BN * cnn);
-        tiles *= cdiv(g.M, BM * cmt);
-        const double wave_eff = static_cast<double>(tiles) / (static_cast<double>(cdiv(static_cast<int>(tiles), sms)) * sms);
-        const double reuse = (cnn == 2 ? 1.0 : 0.8) * (cmt == 2 ? 1.0 : 0.65);  // mt = 1 doubles the dequant work per flop
-        if (wave_eff * reuse > best) {
-          best = wave_eff * reuse;
-          nn = cnn;
-          mt = cmt;
-        }
+        // mt = 1 doubles the dequant work per flop
+        consider(cnn, cmt, false, tiles * cdiv(g.M, BM * cmt), (cnn == 2 ? 1.0 : 0.8) * (cmt == 2 ? 1.0 : 0.65));
       }
   }
   {  // tuning overrides (unset in production)
     static const int env_nn = [] { const char* e = std::getenv("GLOWQ_GEMM_NN"); return e ? std::atoi(e) : 0; }();
     static const int env_mt = [] { const char* e = std::getenv("GLOWQ_GEMM_MT"); return e ? std::atoi(e) : 0; }();
-    if ((env_nn == 1 || env_nn == 2) && !(any_separate && env_nn == 2)) nn = env_nn;
-    if (env_mt == 1 || env_mt == 2) mt = env_mt;
+    if ((env_nn == 1 || env_nn == 2) && !(any_separate && env_nn == 2)) nn = env_nn, pair = false;
+    if (env_mt == 1 || env_mt == 2) mt = env_mt, pair = false;
+    if (env_pair == 1 && !any_separate) pair = true;
+    if (pair) nn = 2, mt = 1;
   }
   GemmParams p{};
   GemmMaps tm;
@@ -801,9 +986,9 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
     const int esz = p.out_fp32 ? 4 : 2;
     d.out_vec_ok = al16(m.out) && ((static_cast<size_t>(m.out_stride) * esz) % 16 == 0);
     d.tile_begin = tile_begin;
-    tile_begin += cdiv(m.OC, BN * nn);
+    tile_begin += cdiv(m.OC, BN * nn * (pair ? 2 : 1));
   }
-  cudaError_t e = launch_gemm(p, tm, nn, stream);
+  cudaError_t e = launch_gemm(p, tm, nn, pair, stream);
   if (e != cudaSuccess) {
     *cuda_err = e;
     return GLOWQ_ERR_CUDA;
