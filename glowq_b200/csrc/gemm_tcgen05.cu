@@ -319,12 +319,17 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = s_tmem_base;
   volatile int* abort_flag = &s_abort;
-  // debug & 2048: CTA 0 records clock64() per role / event / step at workspace + 4096 (tuning only)
+  // Tuning aid, compiled in with -DGLOWQ_GEMM_TRACE only (debug & 2048): CTA (debug >> 12 & 1, 0, 0) records clock64()
+  // per role / event / step at workspace + 4096.
+#ifdef GLOWQ_GEMM_TRACE
   unsigned long long* trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(p.status) - WS_STATUS * 4 + 4096);
   const bool tracing = (p.debug & 2048) && blockIdx.x == ((p.debug >> 12) & 1) && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
   auto tr = [&](int role, int ev, int step) {
     if (tracing && step < 256) trace[(role * 3 + ev) * 256 + step] = clock64();
   };
+#else
+  auto tr = [](int, int, int) {};
+#endif
   // after a failed wait: give the copies of the last `depth` issues a bounded time to land
   auto drain = [&](uint32_t bars, int depth, int issued) {
     for (int j = (issued > depth ? issued - depth : 0); j < issued; ++j) {

@@ -77,13 +77,19 @@ struct Ctx {
   int mode;
 };
 
-// Tuning aid (debug & 16, needs a workspace of at least 40 MB): event e of CTA b -> %globaltimer at workspace + 32 MB.
+// Tuning aid, compiled in with -DGLOWQ_GEMV_TRACE only (debug & 16, needs a workspace of at least 40 MB): event e of
+// CTA b -> %globaltimer at workspace + 32 MB.
 __device__ __forceinline__ void trace_event(const GemvParams& p, int e) {
+#ifdef GLOWQ_GEMV_TRACE
   if (p.debug & 16) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(p.ws_head) + (32u << 20))[blockIdx.x * 16 + e] = t;
   }
+#else
+  (void)p;
+  (void)e;
+#endif
 }
 
 // ---------------------------------------------------------------- activations

@@ -418,3 +418,19 @@ def test_toy_model_through_wrappers_matches_reference(golden_toy, monkeypatch):
     assert tuple(w(x3).shape) == (2, 3, 256)
     w.alpha_svd = 0.0
     torch.testing.assert_close(w(x3), w.inner(x3))
+
+
+@pytest.mark.gpu
+def test_cta_pair_variant_in_subprocess():
+    """The two-CTA (cta_group::2) GEMM variant is opt-in through an environment variable that the library reads
+    once, so it is exercised in a child interpreter: the GEMM parity tests must pass with it forced on."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, GLOWQ_GEMM_PAIR="1")
+    here = os.path.dirname(os.path.abspath(__file__))
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_gpu_parity.py"), "-q", "-x", "-m", "gpu",
+                        "-k", "gemm_parity or gemm_group or shared_memory_weight_tile", "-p", "no:cacheprovider"],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert " passed" in r.stdout
