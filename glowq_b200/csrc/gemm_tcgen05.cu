@@ -94,6 +94,10 @@ struct GemmParams {
   // split-K (only the narrow r = X . R^T product uses it): gridDim.z CTAs share a tile's K steps, each writes its fp32
   // partial tile to its own slot; slot_sum_kernel then adds the slots in slice order
   int ksplit;
+  // swap: up to 128 tokens.  The dequantised weight tile becomes the M side of the MMA (A operand, 128 output columns
+  // per accumulator) and the activation tile its N side (nt = 32, 64 or 128 token rows, B operand): the activation
+  // tile written and re-read per K step shrinks from 128 rows to nt, which is what bounds small token counts.
+  int swap, nt;
   int debug;         // tuning experiments only (0 in production): 16 no copies after the first ring round, 32 no MMA, 64 no dequant
   float* slots;      // [ksplit][tiles][NN * mt * 128 * 128]
   GemmMember mem[kMaxMembers];
@@ -179,6 +183,13 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
       "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
+__device__ __forceinline__ void umma_f16_rt(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 template <int N>
 __device__ __forceinline__ void umma_f16_acc(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc) {  // D += A . B
   constexpr uint32_t kIdesc = (1u << 4) | ((static_cast<uint32_t>(N) >> 3) << 17) | ((BM >> 4) << 24);
@@ -232,6 +243,19 @@ __device__ __forceinline__ void umma2_f16(uint32_t d_tmem, uint64_t a_desc, uint
 __device__ __forceinline__ void umma2_commit(uint32_t cluster_bar) {  // arrives once all MMAs issued so far are done
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
 }
+// one poll of two barriers with both requests in flight together (a poll takes a few hundred clocks to answer)
+__device__ __forceinline__ bool g_mbar_try_both(uint32_t a1, uint32_t parity1, uint32_t a2, uint32_t parity2) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 q, [%3], %4;\n\t"
+      "and.pred p, p, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(a1), "r"(parity1), "r"(a2), "r"(parity2)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -279,7 +303,8 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   const GemmMember& mb = p.mem[mi];
   // n0: first weight row this CTA dequantises; m0: its first token
   const int n0 = PAIR ? (bx - mb.tile_begin) * (2 * BN * NN) + static_cast<int>(crank) * (BN * NN) : (bx - mb.tile_begin) * (BN * NN);
-  const int m0 = PAIR ? blockIdx.y * (2 * BM) + static_cast<int>(crank) * BM : blockIdx.y * (BM * p.mt);
+  const int m0 = PAIR ? blockIdx.y * (2 * BM) + static_cast<int>(crank) * BM
+                      : (p.swap ? blockIdx.y * p.nt : blockIdx.y * (BM * p.mt));
   const int n_mt = (!PAIR && p.mt == 2 && m0 + BM < p.M) ? 2 : 1;
   const int n_nt = PAIR ? 2 : ((NN == 2 && n0 + BN < mb.OC) ? 2 : 1);
   const int nk_all = (p.debug & 1024) ? (p.nk1 + mb.nk2) / 4 : p.nk1 + mb.nk2;
@@ -293,7 +318,9 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       g_mbar_init(full_b + 8 * i, 1);
       g_mbar_init(empty_b + 8 * i, 1);
       // pair: the dequant warps of both CTAs, plus the peer's relay thread (its operand copies have landed)
-      g_mbar_init(bready_b + 8 * i, PAIR ? 2 * Cfg<NN>::kDequantWarps / kPG + 1 : Cfg<NN>::kDequantWarps / kPG);
+      // single CTA: the dequant warps plus the operand producer, whose copies complete their bytes on this barrier too,
+      // so that the MMA thread has ONE barrier to poll per step
+      g_mbar_init(bready_b + 8 * i, 2 * Cfg<NN>::kDequantWarps / kPG + 1 - (PAIR ? 0 : Cfg<NN>::kDequantWarps / kPG));
     }
     for (int i = 0; i < kPStagesG; ++i) {
       g_mbar_init(pfull_b + 8 * i, 1);
@@ -355,14 +382,14 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         tr(0, 0, it - it0);
         if (!(ok = g_mbar_wait(empty_b + 8 * st, ph ^ 1, abort_flag, p.status))) break;
         tr(0, 1, it - it0);
-        const uint32_t sbase = ring + st * kStageG, bar = full_b + 8 * st;
+        const uint32_t sbase = ring + st * kStageG, bar = (PAIR ? full_b : bready_b) + 8 * st;
         const bool phase1 = it < p.nk1;
         const int kk = phase1 ? it : it - p.nk1;
         const bool packed = it < nk_packed;
         if ((p.debug & 16) && it - it0 >= kStagesG) {
           g_mbar_arrive(bar);
         } else {
-          g_mbar_expect_tx(bar, n_mt * kABytes + (packed ? 0 : NN * kBBytes));
+          g_mbar_expect_tx(bar, (p.swap ? p.nt * (BK * 2) : n_mt * kABytes) + (packed ? 0 : NN * kBBytes));
           const CUtensorMap* ta = phase1 ? &tm.a1 : &tm.a2;
           g_tma_2d(sbase, ta, kk * BK, m0, bar);
           if (n_mt == 2) g_tma_2d(sbase + kABytes, ta, kk * BK, m0 + BM, bar);
@@ -375,7 +402,7 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           ph ^= 1;
         }
       }
-      if (!ok) drain(full_b, kStagesG, issued);
+      if (!ok) drain(PAIR ? full_b : bready_b, kStagesG, issued);
     }
     __syncwarp();
   } else if (warp == 2) {
@@ -426,14 +453,28 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           tr(1, 1, it - it0);
         } else {
           if (ok && !g_mbar_try_once(bready_b + 8 * st, ph)) ok = g_mbar_wait(bready_b + 8 * st, ph, abort_flag, p.status);
-          if (ok && !g_mbar_try_once(full_b + 8 * st, ph)) ok = g_mbar_wait(full_b + 8 * st, ph, abort_flag, p.status);
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok && !(skip_mma && it > it0)) {
           const bool phase2 = it >= p.nk1;
           const uint32_t lr_off = (phase2 && mb.lr_separate) ? BN : 0;
           const bool first = phase2 ? (mb.lr_separate && it == p.nk1) : (it == it0);
-          if constexpr (PAIR) {
+          if (!PAIR && p.swap) {
+            // accumulator nn: 128 output columns (TMEM lanes) x nt tokens (TMEM columns nn * nt ..)
+            const uint32_t idesc = (1u << 4) | ((static_cast<uint32_t>(p.nt) >> 3) << 17) | ((BM >> 4) << 24);
+            const uint32_t lr_cols = (phase2 && mb.lr_separate) ? p.nt : 0;
+#pragma unroll
+            for (int nn = 0; nn < NN; ++nn) {
+              if (nn < n_nt) {
+#pragma unroll
+                for (int k16 = 0; k16 < BK / 16; ++k16) {
+                  const uint64_t wd = mk64(desc_lo + boff16 + nn * (kBBytes >> 4) + k16 * 2, desc_hi);
+                  const uint64_t xd = mk64(desc_lo + k16 * 2, desc_hi);
+                  umma_f16_rt(tmem_base + nn * p.nt + lr_cols, wd, xd, idesc, (first && k16 == 0) ? 0u : 1u);
+                }
+              }
+            }
+          } else if constexpr (PAIR) {
             // accumulator n (TMEM columns 256 n ..): B rows 128 n .. of this CTA and of the peer, 256 columns in all
 #pragma unroll
             for (int n = 0; n < 2; ++n) {
@@ -545,8 +586,10 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       const bool packed = it < nk_packed;
       if (tr_warp) tr(2, 0, it - it0);
       if (lane == 0) {  // one lane polls: the packed tile has landed, and the MMAs that read this B slot are done
-        if (packed) ok = ok && g_mbar_wait(pfull_b + 8 * sp, pph, abort_flag, p.status);
-        ok = ok && g_mbar_wait(empty_b + 8 * st, ph ^ 1, abort_flag, p.status);
+        if (!(packed && ok && g_mbar_try_both(pfull_b + 8 * sp, pph, empty_b + 8 * st, ph ^ 1))) {
+          if (packed) ok = ok && g_mbar_wait(pfull_b + 8 * sp, pph, abort_flag, p.status);
+          ok = ok && g_mbar_wait(empty_b + 8 * st, ph ^ 1, abort_flag, p.status);
+        }
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (tr_warp) tr(2, 1, it - it0);
@@ -661,7 +704,39 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     const size_t kSlotFloats = static_cast<size_t>(NN) * p.mt * BM * BN;
     const size_t tile_lin = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
     const size_t n_tiles_all = static_cast<size_t>(gridDim.x) * gridDim.y;
-    if constexpr (PAIR) {
+    if (!PAIR && p.swap) {
+      // TMEM lane = output column, TMEM column = token: for a fixed token the 32 lanes of a warp store 32 consecutive
+      // output columns (one 64-byte segment in fp16)
+      const int units = NN * (p.nt >> 5);
+      const int col_l = q * 32 + lane;
+      for (int u = (warp - Cfg<NN>::kCtrlWarps) >> 2; u < units; u += kWays) {
+        const int nn = u / (p.nt >> 5), cb = u - nn * (p.nt >> 5);
+        if (nn >= n_nt) continue;
+        uint32_t acc[32], lr[32];
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + nn * p.nt + cb * 32;
+        tmem_ld32(taddr, acc);
+        if (NN == 1 && mb.lr_separate) tmem_ld32(taddr + p.nt, lr);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int col = n0 + nn * BN + col_l;
+        if (ok && col < mb.OC) {
+          const float bias = mb.bias ? __half2float(mb.bias[col]) : 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int tok = m0 + cb * 32 + j;
+            if (tok < p.M) {
+              float v = __uint_as_float(acc[j]);
+              if (NN == 1 && mb.lr_separate) v = fmaf(mb.alpha, __uint_as_float(lr[j]), v);
+              v += bias;
+              const size_t idx = static_cast<size_t>(tok) * mb.out_stride + col;
+              if (p.out_fp32)
+                static_cast<float*>(mb.out)[idx] = v;
+              else
+                static_cast<__half*>(mb.out)[idx] = __float2half_rn(v);
+            }
+          }
+        }
+      }
+    } else if constexpr (PAIR) {
       // two accumulators of 256 columns: column c of accumulator n is output column 128 n + c of this pair tile when
       // c < 128 (rows CTA 0 dequantised), 256 + 128 n + (c - 128) otherwise (CTA 1's rows); 16 blocks of 32 columns
       const int tile_n0 = (bx - mb.tile_begin) * (2 * BN * NN);
@@ -917,6 +992,10 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
   int nn = 1, mt = 2;
   bool pair = false;
   static const int env_pair = [] { const char* e = std::getenv("GLOWQ_GEMM_PAIR"); return e ? std::atoi(e) : -1; }();
+  static const int env_swap = [] { const char* e = std::getenv("GLOWQ_GEMM_SWAP"); return e ? std::atoi(e) : -1; }();
+  // Up to 128 tokens: weights on the M side of the MMA, tokens on its N side (see GemmParams::swap).
+  const bool swap = g.M <= BM && env_swap != 0;
+  const int nt = g.M <= 32 ? 32 : (g.M <= 64 ? 64 : BM);
   {
     int sms = 148, dev = 0;
     cudaGetDevice(&dev);
@@ -937,19 +1016,22 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
       consider(2, 1, true, 2 * tiles * cdiv(g.M, 2 * BM), 1.3);
     }
     for (int cnn = any_separate ? 1 : 2; cnn >= 1; --cnn)
-      for (int cmt = 2; cmt >= 1; --cmt) {
+      for (int cmt = swap ? 1 : 2; cmt >= 1; --cmt) {
         long tiles = 0;
         for (int i = 0; i < g.n_members; ++i) tiles += cdiv(g.members[i].OC, BN * cnn);
         // mt = 1 doubles the dequant work per flop
-        consider(cnn, cmt, false, tiles * cdiv(g.M, BM * cmt), (cnn == 2 ? 1.0 : 0.8) * (cmt == 2 ? 1.0 : 0.65));
+        if (swap)
+          consider(cnn, 1, false, tiles, cnn == 2 ? 1.0 : 0.9);
+        else
+          consider(cnn, cmt, false, tiles * cdiv(g.M, BM * cmt), (cnn == 2 ? 1.0 : 0.8) * (cmt == 2 ? 1.0 : 0.65));
       }
   }
   {  // tuning overrides (unset in production)
     static const int env_nn = [] { const char* e = std::getenv("GLOWQ_GEMM_NN"); return e ? std::atoi(e) : 0; }();
     static const int env_mt = [] { const char* e = std::getenv("GLOWQ_GEMM_MT"); return e ? std::atoi(e) : 0; }();
     if ((env_nn == 1 || env_nn == 2) && !(any_separate && env_nn == 2)) nn = env_nn, pair = false;
-    if (env_mt == 1 || env_mt == 2) mt = env_mt, pair = false;
-    if (env_pair == 1 && !any_separate) pair = true;
+    if ((env_mt == 1 || env_mt == 2) && !swap) mt = env_mt, pair = false;
+    if (env_pair == 1 && !any_separate && !swap) pair = true;
     if (pair) nn = 2, mt = 1;
   }
   GemmParams p{};
@@ -957,6 +1039,16 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
   std::memset(&tm, 0, sizeof(tm));
   tm.a1 = tm_x;
   tm.a2 = any_corr ? tm_r : tm_x;
+  if (swap) {  // activation boxes of nt token rows
+    if ((rc = map(&tm.a1, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.x, g.IC, g.M, static_cast<uint64_t>(g.x_stride) * 2, BK, nt, 1)))
+      return rc;
+    tm.a2 = tm.a1;
+    if (any_corr && (rc = map(&tm.a2, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.r_buf, g.rank, g.M,
+                              static_cast<uint64_t>(g.rank) * 2, BK, nt, 1)))
+      return rc;
+    p.swap = 1;
+    p.nt = nt;
+  }
   p.status = status;
   p.M = g.M;
   p.nk1 = cdiv(g.IC, BK);
