@@ -993,8 +993,10 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
   bool pair = false;
   static const int env_pair = [] { const char* e = std::getenv("GLOWQ_GEMM_PAIR"); return e ? std::atoi(e) : -1; }();
   static const int env_swap = [] { const char* e = std::getenv("GLOWQ_GEMM_SWAP"); return e ? std::atoi(e) : -1; }();
-  // Up to 128 tokens: weights on the M side of the MMA, tokens on its N side (see GemmParams::swap).
-  const bool swap = g.M <= BM && env_swap != 0;
+  // Up to 128 tokens: weights on the M side of the MMA, tokens on its N side (see GemmParams::swap).  Measured no
+  // faster than tokens on the M side (31.5 vs 30.3 us for Llama-3.2-3B gate/up at 32 tokens): at these sizes the MMA
+  // thread's issue rate sets the pace, and N = 256 instructions need half as many issues per weight row.  Opt-in.
+  const bool swap = g.M <= BM && env_swap == 1;
   const int nt = g.M <= 32 ? 32 : (g.M <= 64 ? 64 : BM);
   {
     int sms = 148, dev = 0;

@@ -422,12 +422,13 @@ def test_toy_model_through_wrappers_matches_reference(golden_toy, monkeypatch):
 
 @pytest.mark.gpu
 def test_cta_pair_variant_in_subprocess():
-    """The two-CTA (cta_group::2) GEMM variant is opt-in through an environment variable that the library reads
-    once, so it is exercised in a child interpreter: the GEMM parity tests must pass with it forced on."""
+    """The two-CTA (cta_group::2) GEMM variant (above 128 tokens) and the swapped-operand variant (up to 128 tokens)
+    are opt-in through environment variables that the library reads once, so they are exercised in a child
+    interpreter: the GEMM parity tests must pass with both forced on."""
     import os
     import subprocess
     import sys
-    env = dict(os.environ, GLOWQ_GEMM_PAIR="1")
+    env = dict(os.environ, GLOWQ_GEMM_PAIR="1", GLOWQ_GEMM_SWAP="1")
     here = os.path.dirname(os.path.abspath(__file__))
     r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_gpu_parity.py"), "-q", "-x", "-m", "gpu",
                         "-k", "gemm_parity or gemm_group or shared_memory_weight_tile", "-p", "no:cacheprovider"],
