@@ -441,22 +441,11 @@ int glowq_w4a16_group_forward(const glowq_w4a16_group_t* group) {
   if (g.M == 0) return GLOWQ_OK;
   cudaStream_t stream = static_cast<cudaStream_t>(g.stream);
   // Measured on B200: 8 tokens stream at the cost of one, so M tokens cost ceil(M/8) streaming launches.  The tcgen05
-  // GEMM takes about the same time for anything up to 128 tokens (it is bound by moving each dequantised weight tile
-  // through shared memory once: ~0.45 us per 64 columns of K and wave of tiles).  At 17-24 tokens (3 streaming
-  // launches) it wins for the wide projections only (Llama-3.2-3B gate/up: 30 us vs 44 us; q/k/v: 30 vs 30; o: 30 vs
-  // 24); at 25-32 tokens it wins except for long rows (down_proj, K = 8192: 65 us vs 62 us); above 32 everywhere.
+  // GEMM (K-sliced over all SMs when it has few tiles) takes about the same time for anything up to 128 tokens.  At
+  // 16 tokens (two streaming launches) the two are level (Llama-3.2-3B q/k/v: 20 vs 17 us plain, 26 vs 26 corrected;
+  // gate/up: 30 vs 30); from 17 tokens (three launches) the GEMM wins everywhere.
   bool use_gemm = g.kernel == GLOWQ_KERNEL_GEMM;
-  if (g.kernel == GLOWQ_KERNEL_AUTO) {
-    double weights = 0;
-    for (int i = 0; i < g.n_members; ++i) weights += static_cast<double>(g.members[i].OC) * g.IC;
-    const bool long_rows = g.IC >= 8192;
-    if (g.M > 32)
-      use_gemm = true;
-    else if (g.M > 24)
-      use_gemm = !long_rows || weights >= 1.0e8;
-    else if (g.M > kGemvAutoMaxM)
-      use_gemm = weights >= 1.0e8 || (weights >= 4.0e7 && !long_rows);
-  }
+  if (g.kernel == GLOWQ_KERNEL_AUTO) use_gemm = g.M > kGemvAutoMaxM;
   if (use_gemm && gemm_supported(g)) {
     cudaError_t ce = cudaSuccess;
     rc = gemm_group_forward(g, stream, &ce);

@@ -99,7 +99,8 @@ struct GemmParams {
   // tile written and re-read per K step shrinks from 128 rows to nt, which is what bounds small token counts.
   int swap, nt;
   int debug;         // tuning experiments only (0 in production): 16 no copies after the first ring round, 32 no MMA, 64 no dequant
-  float* slots;      // [ksplit][tiles][NN * mt * 128 * 128]
+  float* slots;      // [ksplit][tiles][NN * mt][slot_rows][128]
+  int slot_rows;     // token rows kept per 128 x 128 accumulator in a slot (a multiple of 32, >= the tile's valid tokens)
   GemmMember mem[kMaxMembers];
 };
 struct alignas(64) GemmMaps {
@@ -701,7 +702,7 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         }
       }
     };
-    const size_t kSlotFloats = static_cast<size_t>(NN) * p.mt * BM * BN;
+    const size_t kSlotFloats = static_cast<size_t>(NN) * p.mt * p.slot_rows * BN;
     const size_t tile_lin = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
     const size_t n_tiles_all = static_cast<size_t>(gridDim.x) * gridDim.y;
     if (!PAIR && p.swap) {
@@ -779,7 +780,7 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           }
           if (p.ksplit > 1) {
             float* sl = p.slots + (static_cast<size_t>(blockIdx.z) * n_tiles_all + tile_lin) * kSlotFloats +
-                        static_cast<size_t>(at) * (BM * BN) + (q * 32 + lane) * BN + cb * 32;
+                        static_cast<size_t>(nn * p.mt + mt) * (p.slot_rows * BN) + (q * 32 + lane) * BN + cb * 32;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) __stcg(reinterpret_cast<float4*>(sl + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
           } else {
@@ -825,6 +826,49 @@ __global__ void slot_sum_kernel(const float* __restrict__ slots, __half* __restr
   pk.x = *reinterpret_cast<uint32_t*>(&lo);
   pk.y = *reinterpret_cast<uint32_t*>(&hi);
   *reinterpret_cast<uint2*>(out + static_cast<size_t>(tok) * out_stride + col) = pk;
+}
+
+// Split-K of a group GEMM (mt = 1, up to two token tiles): out[tok, col .. col + 3] of the member that owns column tile `tile`
+// = sum over K slices of the slot tiles (in slice order) + bias.
+__global__ void slot_sum_members_kernel(const __grid_constant__ GemmParams p, int nn, int n_tiles, int m_tiles) {
+  const int per_tile = nn * p.slot_rows * (BN / 4);
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= m_tiles * n_tiles * per_tile) return;
+  const int tile_lin = idx / per_tile;              // token tile (of 128) major, column tile minor: the grid's order
+  const int ty = tile_lin / n_tiles, tile = tile_lin - ty * n_tiles;
+  int rem = idx - tile_lin * per_tile;
+  const int at = rem / (p.slot_rows * (BN / 4));
+  rem -= at * (p.slot_rows * (BN / 4));
+  const int row = rem / (BN / 4), c4 = (rem - row * (BN / 4)) * 4;
+  const int tok = ty * BM + row;
+  int mi = 0;
+  for (int i = 1; i < kMaxMembers; ++i)
+    if (i < p.n_members && tile >= p.mem[i].tile_begin) mi = i;
+  const GemmMember& mb = p.mem[mi];
+  const int col = (tile - mb.tile_begin) * (BN * nn) + at * BN + c4;
+  if (tok >= p.M || col >= mb.OC) return;
+  const size_t slot_floats = static_cast<size_t>(nn) * p.slot_rows * BN;
+  const size_t in_slot = static_cast<size_t>(at) * (p.slot_rows * BN) + static_cast<size_t>(row) * BN + c4;
+  const size_t tiles_all = static_cast<size_t>(n_tiles) * m_tiles;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int z = 0; z < p.ksplit; ++z) {
+    const float4 t = __ldcg(reinterpret_cast<const float4*>(p.slots + (static_cast<size_t>(z) * tiles_all + tile_lin) * slot_floats + in_slot));
+    acc.x += t.x;
+    acc.y += t.y;
+    acc.z += t.z;
+    acc.w += t.w;
+  }
+  float v[4] = {acc.x, acc.y, acc.z, acc.w};
+  const size_t o = static_cast<size_t>(tok) * mb.out_stride + col;
+  for (int j = 0; j < 4; ++j) {
+    if (col + j < mb.OC) {
+      const float r = v[j] + (mb.bias ? __half2float(mb.bias[col + j]) : 0.f);
+      if (p.out_fp32)
+        static_cast<float*>(mb.out)[o + j] = r;
+      else
+        static_cast<__half*>(mb.out)[o + j] = __float2half_rn(r);
+    }
+  }
 }
 
 inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -910,9 +954,27 @@ inline size_t counters_end(int OC_total, int n_members) {
   return (n + 255) & ~static_cast<size_t>(255);
 }
 
+// K slices of a group GEMM with few tiles (up to 128 tokens): planned for 148 SMs so that the workspace size does not
+// depend on the device.
+constexpr int kPlanSms = 148;
+inline int main_ksplit(int tiles, int nk, int sms) {
+  if (tiles * 2 > sms) return 1;
+  return std::max(1, std::min({8, sms / tiles, nk / 8}));
+}
+inline int slot_rows_for(int M) { return std::min(BM, ((M + 31) / 32) * 32); }
+inline size_t main_slot_bytes_bound(int M, int IC, int OC_total, int n_members) {
+  // (up to 16 tokens the automatic choice never takes this kernel; a forced call then runs without slicing)
+  const int m_tiles = cdiv(M, BM);
+  if (M <= 16 || M > 2 * BM || cdiv(OC_total, 2 * BN) * m_tiles * 2 > kPlanSms) return 0;
+  const int tiles_ub = (cdiv(OC_total, BN) + n_members) * m_tiles;  // 128 x 128 tiles
+  const int slots_ub = std::min(8 * tiles_ub, kPlanSms + tiles_ub);
+  return static_cast<size_t>(slots_ub) * slot_rows_for(M) * BN * 4;
+}
+
 size_t gemm_workspace_bytes(int M, int IC, int OC_total, int rank, int n_members) {
-  if (rank <= 0) return kWsHeaderBytes;
-  return counters_end(OC_total, n_members) + r_slot_bytes(M, IC, rank) + 256;
+  const size_t slots = std::max(rank > 0 ? r_slot_bytes(M, IC, rank) : 0, main_slot_bytes_bound(M, IC, OC_total, n_members));
+  if (slots == 0) return kWsHeaderBytes;
+  return counters_end(OC_total, n_members) + slots + 256;
 }
 
 int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaError_t* cuda_err) {
@@ -958,6 +1020,7 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
       slot_off = kWsHeaderBytes;
     }
     p.slots = reinterpret_cast<float*>(static_cast<unsigned char*>(g.workspace) + slot_off);
+    p.slot_rows = BM;
     p.mem[0].out = g.r_buf;
     p.mem[0].OC = g.rank;
     p.mem[0].out_stride = g.rank;
@@ -1028,6 +1091,33 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
           consider(cnn, cmt, false, tiles * cdiv(g.M, BM * cmt), (cnn == 2 ? 1.0 : 0.8) * (cmt == 2 ? 1.0 : 0.65));
       }
   }
+  static const int env_ks = [] { const char* e = std::getenv("GLOWQ_GEMM_KSPLIT"); return e ? std::atoi(e) : -1; }();
+  if (g.M <= 2 * BM && !any_separate && !swap && env_ks != 0) {
+    // Up to 256 tokens a CTA's K-step rate bounds the launch, not the flops: pick the column-tile width together with
+    // the K slicing, by steps per CTA x relative step time (a 256-column step takes about 4/3 of a 128-column one).
+    int sms = kPlanSms, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int nk = cdiv(g.IC, BK);
+    double best_cost = 1e30;
+    for (int cnn = 2; cnn >= 1; --cnn)
+      for (int cmt = 1; cmt <= (g.M > BM ? 2 : 1); ++cmt) {
+        int tiles = 0;
+        for (int i = 0; i < g.n_members; ++i) tiles += cdiv(g.members[i].OC, BN * cnn);
+        tiles *= cdiv(g.M, BM * cmt);
+        const int ks = cmt == 1 ? main_ksplit(tiles, nk, std::min(sms, kPlanSms)) : 1;  // slices are written per 128 tokens
+        const double step = cmt == 2 ? (cnn == 2 ? 1.45 : 1.05) : (cnn == 2 ? 1.0 : 0.75);  // measured clocks per step, relative
+        // + the fp32 slot traffic of a sliced launch, in step equivalents
+        const double cost = static_cast<double>(cdiv(tiles * ks, sms)) * cdiv(nk, ks) * step +
+                            (ks > 1 ? 14.0 * slot_rows_for(g.M) / BM : 0.0);
+        if (cost < best_cost) {
+          best_cost = cost;
+          nn = cnn;
+          mt = cmt;
+          pair = false;
+        }
+      }
+  }
   {  // tuning overrides (unset in production)
     static const int env_nn = [] { const char* e = std::getenv("GLOWQ_GEMM_NN"); return e ? std::atoi(e) : 0; }();
     static const int env_mt = [] { const char* e = std::getenv("GLOWQ_GEMM_MT"); return e ? std::atoi(e) : 0; }();
@@ -1057,7 +1147,32 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
   p.w4 = 1;
   p.out_fp32 = g.out_dtype == GLOWQ_OUT_F32;
   p.n_members = g.n_members;
+  // Few tiles and few tokens: slice K over gridDim.z so that all SMs stream weights (a CTA's step rate, not the
+  // amount of work, bounds small token counts), and add the slices up afterwards.
+  int ksplit = 1;
+  size_t main_slot_off = 0;
+  if (!pair && !swap && !any_separate && g.M <= 2 * BM && mt == 1 && env_ks != 0) {
+    int sms = kPlanSms, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    long tiles = 0;
+    for (int i = 0; i < g.n_members; ++i) tiles += cdiv(g.members[i].OC, BN * nn);
+    tiles *= cdiv(g.M, BM);
+    ksplit = main_ksplit(static_cast<int>(tiles), cdiv(g.IC, BK), std::min(sms, kPlanSms));
+    if (env_ks > 0) ksplit = std::min(env_ks, std::max(1, cdiv(g.IC, BK) / 2));
+    if (ksplit > 1) {
+      int oc_total = 0;
+      for (int i = 0; i < g.n_members; ++i) oc_total += g.members[i].OC;
+      const size_t need = static_cast<size_t>(ksplit) * tiles * nn * slot_rows_for(g.M) * BN * 4;
+      main_slot_off = g.workspace_bytes >= need ? ((g.workspace_bytes - need) & ~static_cast<size_t>(255)) : 0;
+      if (main_slot_off < counters_end(oc_total, g.n_members)) ksplit = 1;  // workspace not sized for slicing
+    }
+    if (ksplit > 1) mt = 1;
+  }
   p.mt = mt;
+  p.ksplit = ksplit;
+  p.slot_rows = slot_rows_for(g.M);
+  p.slots = reinterpret_cast<float*>(static_cast<unsigned char*>(g.workspace) + main_slot_off);
   p.debug = g.reserved;
   int tile_begin = 0;
   for (int i = 0; i < g.n_members; ++i) {
@@ -1088,6 +1203,12 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
     tile_begin += cdiv(m.OC, BN * nn * (pair ? 2 : 1));
   }
   cudaError_t e = launch_gemm(p, tm, nn, pair, stream);
+  if (e == cudaSuccess && p.ksplit > 1) {
+    const int m_tiles = cdiv(g.M, BM);
+    const int n = m_tiles * tile_begin * nn * p.slot_rows * (BN / 4);
+    slot_sum_members_kernel<<<cdiv(n, 256), 256, 0, stream>>>(p, nn, tile_begin, m_tiles);
+    e = cudaGetLastError();
+  }
   if (e != cudaSuccess) {
     *cuda_err = e;
     return GLOWQ_ERR_CUDA;
