@@ -281,6 +281,8 @@ __global__ void __launch_bounds__(Cfg<NN>::kThreads, 1)
 gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ GemmMaps tm) {
   static_assert(!PAIR || NN == 2, "the CTA pair works on two 128-row weight tiles per CTA");
   constexpr int kPG = PAIR ? Cfg<NN>::kPairPassGroups : Cfg<NN>::kPassGroups;
+  // let the next kernel of the stream start its prologue and its weight prefetch as SMs free up
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int kStagesG = p.stages, kPStagesG = p.pstages;
   const uint32_t kBOff = p.mt * kABytes;              // B tiles inside an operand stage
   const uint32_t kStageG = kBOff + NN * kBBytes;      // operand stage: mt activation tiles + NN weight tiles
@@ -379,6 +381,9 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       uint32_t st = 0, ph = 0;
       int issued = 0;
       bool ok = true;
+      // activations, r and (for the r product) nothing else of this thread's copies may be read before the earlier
+      // kernels of the stream are complete; the packed-weight producer and the dequant warps do not wait
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       for (int it = it0; it < nk; ++it) {
         tr(0, 0, it - it0);
         if (!(ok = g_mbar_wait(empty_b + 8 * st, ph ^ 1, abort_flag, p.status))) break;
@@ -807,6 +812,8 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
 // out[tok, col..col+3] = half(sum over slices of the 128 x 128 fp32 slot tiles), slices added in order.
 __global__ void slot_sum_kernel(const float* __restrict__ slots, __half* __restrict__ out, int M, int N, int out_stride,
                                 int ksplit, int tiles_x, int tiles_all) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the slots come from the kernel before
   const int quads = N >> 2;
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= M * quads) return;
@@ -831,6 +838,8 @@ __global__ void slot_sum_kernel(const float* __restrict__ slots, __half* __restr
 // Split-K of a group GEMM (mt = 1, up to two token tiles): out[tok, col .. col + 3] of the member that owns column tile `tile`
 // = sum over K slices of the slot tiles (in slice order) + bias.
 __global__ void slot_sum_members_kernel(const __grid_constant__ GemmParams p, int nn, int n_tiles, int m_tiles) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the slots come from the kernel before
   const int per_tile = nn * p.slot_rows * (BN / 4);
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= m_tiles * n_tiles * per_tile) return;
@@ -874,6 +883,31 @@ __global__ void slot_sum_members_kernel(const __grid_constant__ GemmParams p, in
 inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int cdiv(int a, int b) { return (a + b - 1) / b; }
 
+// Programmatic dependent launch: a kernel of this file may start while its predecessor in the stream is still
+// running; it touches nothing the predecessor may still write (activations, r, slots) before griddepcontrol.wait.
+// GLOWQ_PDL=0 falls back to plain stream order.
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("GLOWQ_PDL");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 template <int NN, bool PAIR>
 cudaError_t launch_gemm_nn(const GemmParams& p, const GemmMaps& tm, cudaStream_t stream) {
   static bool attr_done[64] = {};
@@ -894,8 +928,7 @@ cudaError_t launch_gemm_nn(const GemmParams& p, const GemmMaps& tm, cudaStream_t
   if (q.ksplit < 1) q.ksplit = 1;
   if (!PAIR) {
     dim3 grid(n_tiles, cdiv(p.M, BM * p.mt), q.ksplit);
-    gemm_w4a16_kernel<NN, false><<<grid, Cfg<NN>::kThreads, Cfg<NN>::smem(p.mt), stream>>>(q, tm);
-    return cudaGetLastError();
+    return launch_pdl(gemm_w4a16_kernel<NN, false>, grid, dim3(Cfg<NN>::kThreads), Cfg<NN>::smem(p.mt), stream, q, tm);
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * n_tiles, cdiv(p.M, 2 * BM), 1);  // clusters of two CTAs along x
@@ -1029,9 +1062,8 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
     cudaError_t e = launch_gemm(p, tm, 1, false, stream);
     if (e == cudaSuccess && p.ksplit > 1) {
       const int tiles_x = cdiv(g.rank, BN), tiles_all = tiles_x * cdiv(g.M, BM), n = g.M * (g.rank >> 2);
-      slot_sum_kernel<<<cdiv(n, 256), 256, 0, stream>>>(p.slots, static_cast<__half*>(g.r_buf), g.M, g.rank, g.rank, p.ksplit,
-                                                        tiles_x, tiles_all);
-      e = cudaGetLastError();
+      e = launch_pdl(slot_sum_kernel, dim3(cdiv(n, 256)), dim3(256), 0, stream, static_cast<const float*>(p.slots),
+                     static_cast<__half*>(g.r_buf), g.M, g.rank, g.rank, p.ksplit, tiles_x, tiles_all);
     }
     if (e != cudaSuccess) {
       *cuda_err = e;
@@ -1206,8 +1238,7 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
   if (e == cudaSuccess && p.ksplit > 1) {
     const int m_tiles = cdiv(g.M, BM);
     const int n = m_tiles * tile_begin * nn * p.slot_rows * (BN / 4);
-    slot_sum_members_kernel<<<cdiv(n, 256), 256, 0, stream>>>(p, nn, tile_begin, m_tiles);
-    e = cudaGetLastError();
+    e = launch_pdl(slot_sum_members_kernel, dim3(cdiv(n, 256)), dim3(256), 0, stream, p, nn, tile_begin, m_tiles);
   }
   if (e != cudaSuccess) {
     *cuda_err = e;
