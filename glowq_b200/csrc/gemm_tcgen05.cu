@@ -99,7 +99,12 @@ struct GemmParams {
   // tile written and re-read per K step shrinks from 128 rows to nt, which is what bounds small token counts.
   int swap, nt;
   int debug;         // tuning experiments only (0 in production): 16 no copies after the first ring round, 32 no MMA, 64 no dequant
-  float* slots;      // [ksplit][tiles][NN * mt][slot_rows][128]
+  // Work items (blockIdx.x, single-CTA kernels): tiles [0, full_tiles) are computed whole; each of the n_tail tiles
+  // after them is cut into ksplit K slices (item = full_tiles + tail index * ksplit + slice).  Tiles are numbered
+  // token tile major, column tile minor (n_x column tiles).  full_tiles = 0 slices every tile (few tokens);
+  // full_tiles = whole waves slices only the last, partial wave of a large launch.
+  int full_tiles, n_tail, n_x;
+  float* slots;      // [ksplit][n_tail][NN * mt][slot_rows][128]
   int slot_rows;     // token rows kept per 128 x 128 accumulator in a slot (a multiple of 32, >= the tile's valid tokens)
   GemmMember mem[kMaxMembers];
 };
@@ -298,7 +303,20 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   const uint32_t pring = ring + kStagesG * kStageG;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t crank = PAIR ? cluster_ctarank() : 0u;   // 0: the CTA that issues the MMAs
-  const int bx = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);  // column tile index
+  int tile_lin = 0, zslice = 0, ks = 1;   // (single CTA) tile, K slice and slice count of this work item
+  if (!PAIR) {
+    const int item = static_cast<int>(blockIdx.x);
+    if (item < p.full_tiles) {
+      tile_lin = item;
+    } else {
+      const int r = item - p.full_tiles, t = r / p.ksplit;
+      tile_lin = p.full_tiles + t;
+      zslice = r - t * p.ksplit;
+      ks = p.ksplit;
+    }
+  }
+  const int by = PAIR ? static_cast<int>(blockIdx.y) : tile_lin / p.n_x;                        // token tile index
+  const int bx = PAIR ? static_cast<int>(blockIdx.x >> 1) : tile_lin - by * p.n_x;              // column tile index
   int mi = 0;
 #pragma unroll
   for (int i = 1; i < kMaxMembers; ++i)
@@ -306,13 +324,12 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   const GemmMember& mb = p.mem[mi];
   // n0: first weight row this CTA dequantises; m0: its first token
   const int n0 = PAIR ? (bx - mb.tile_begin) * (2 * BN * NN) + static_cast<int>(crank) * (BN * NN) : (bx - mb.tile_begin) * (BN * NN);
-  const int m0 = PAIR ? blockIdx.y * (2 * BM) + static_cast<int>(crank) * BM
-                      : (p.swap ? blockIdx.y * p.nt : blockIdx.y * (BM * p.mt));
+  const int m0 = PAIR ? by * (2 * BM) + static_cast<int>(crank) * BM : (p.swap ? by * p.nt : by * (BM * p.mt));
   const int n_mt = (!PAIR && p.mt == 2 && m0 + BM < p.M) ? 2 : 1;
   const int n_nt = PAIR ? 2 : ((NN == 2 && n0 + BN < mb.OC) ? 2 : 1);
   const int nk_all = (p.debug & 1024) ? (p.nk1 + mb.nk2) / 4 : p.nk1 + mb.nk2;
-  const int it0 = p.ksplit > 1 ? static_cast<int>(static_cast<long long>(nk_all) * blockIdx.z / p.ksplit) : 0;
-  const int nk = p.ksplit > 1 ? static_cast<int>(static_cast<long long>(nk_all) * (blockIdx.z + 1) / p.ksplit) : nk_all;
+  const int it0 = ks > 1 ? static_cast<int>(static_cast<long long>(nk_all) * zslice / ks) : 0;
+  const int nk = ks > 1 ? static_cast<int>(static_cast<long long>(nk_all) * (zslice + 1) / ks) : nk_all;
   const int nk_packed = p.w4 ? min(nk, p.nk1) : it0;  // steps [it0, nk_packed) dequantise a packed tile
 
   if (threadIdx.x == 0) {
@@ -353,7 +370,7 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   // per role / event / step at workspace + 4096.
 #ifdef GLOWQ_GEMM_TRACE
   unsigned long long* trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(p.status) - WS_STATUS * 4 + 4096);
-  const bool tracing = (p.debug & 2048) && blockIdx.x == ((p.debug >> 12) & 1) && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
+  const bool tracing = (p.debug & 2048) && blockIdx.x == ((p.debug >> 12) & 1) && blockIdx.y == 0 && lane == 0;
   auto tr = [&](int role, int ev, int step) {
     if (tracing && step < 256) trace[(role * 3 + ev) * 256 + step] = clock64();
   };
@@ -708,8 +725,6 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       }
     };
     const size_t kSlotFloats = static_cast<size_t>(NN) * p.mt * p.slot_rows * BN;
-    const size_t tile_lin = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
-    const size_t n_tiles_all = static_cast<size_t>(gridDim.x) * gridDim.y;
     if (!PAIR && p.swap) {
       // TMEM lane = output column, TMEM column = token: for a fixed token the 32 lanes of a warp store 32 consecutive
       // output columns (one 64-byte segment in fp16)
@@ -783,8 +798,8 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
             v[j] = __uint_as_float(acc[j]);
             if (NN == 1 && mb.lr_separate) v[j] = fmaf(mb.alpha, __uint_as_float(lr[j]), v[j]);
           }
-          if (p.ksplit > 1) {
-            float* sl = p.slots + (static_cast<size_t>(blockIdx.z) * n_tiles_all + tile_lin) * kSlotFloats +
+          if (ks > 1) {
+            float* sl = p.slots + (static_cast<size_t>(zslice) * p.n_tail + (tile_lin - p.full_tiles)) * kSlotFloats +
                         static_cast<size_t>(nn * p.mt + mt) * (p.slot_rows * BN) + (q * 32 + lane) * BN + cb * 32;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) __stcg(reinterpret_cast<float4*>(sl + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
@@ -835,33 +850,33 @@ __global__ void slot_sum_kernel(const float* __restrict__ slots, __half* __restr
   *reinterpret_cast<uint2*>(out + static_cast<size_t>(tok) * out_stride + col) = pk;
 }
 
-// Split-K of a group GEMM (mt = 1, up to two token tiles): out[tok, col .. col + 3] of the member that owns column tile `tile`
-// = sum over K slices of the slot tiles (in slice order) + bias.
-__global__ void slot_sum_members_kernel(const __grid_constant__ GemmParams p, int nn, int n_tiles, int m_tiles) {
+// K-sliced tiles of a group GEMM: out[tok, col .. col + 3] of the member that owns the tile's columns = sum over the K
+// slices of the slot tiles (in slice order) + bias.  One thread per 4 columns of a sliced tile.
+__global__ void slot_sum_members_kernel(const __grid_constant__ GemmParams p, int nn) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");  // the slots come from the kernel before
-  const int per_tile = nn * p.slot_rows * (BN / 4);
+  const int per_blk = p.slot_rows * (BN / 4), per_tile = nn * p.mt * per_blk;
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= m_tiles * n_tiles * per_tile) return;
-  const int tile_lin = idx / per_tile;              // token tile (of 128) major, column tile minor: the grid's order
-  const int ty = tile_lin / n_tiles, tile = tile_lin - ty * n_tiles;
-  int rem = idx - tile_lin * per_tile;
-  const int at = rem / (p.slot_rows * (BN / 4));
-  rem -= at * (p.slot_rows * (BN / 4));
+  if (idx >= p.n_tail * per_tile) return;
+  const int tail = idx / per_tile;
+  int rem = idx - tail * per_tile;
+  const int blk = rem / per_blk;                    // accumulator of the tile: column block major, token block minor
+  rem -= blk * per_blk;
   const int row = rem / (BN / 4), c4 = (rem - row * (BN / 4)) * 4;
-  const int tok = ty * BM + row;
+  const int tile_lin = p.full_tiles + tail, ty = tile_lin / p.n_x, tile = tile_lin - ty * p.n_x;
+  const int nn_i = blk / p.mt, mt_i = blk - nn_i * p.mt;
+  const int tok = ty * (BM * p.mt) + mt_i * BM + row;
   int mi = 0;
   for (int i = 1; i < kMaxMembers; ++i)
     if (i < p.n_members && tile >= p.mem[i].tile_begin) mi = i;
   const GemmMember& mb = p.mem[mi];
-  const int col = (tile - mb.tile_begin) * (BN * nn) + at * BN + c4;
+  const int col = (tile - mb.tile_begin) * (BN * nn) + nn_i * BN + c4;
   if (tok >= p.M || col >= mb.OC) return;
-  const size_t slot_floats = static_cast<size_t>(nn) * p.slot_rows * BN;
-  const size_t in_slot = static_cast<size_t>(at) * (p.slot_rows * BN) + static_cast<size_t>(row) * BN + c4;
-  const size_t tiles_all = static_cast<size_t>(n_tiles) * m_tiles;
+  const size_t slot_floats = static_cast<size_t>(nn) * p.mt * p.slot_rows * BN;
+  const size_t in_slot = static_cast<size_t>(blk) * (p.slot_rows * BN) + static_cast<size_t>(row) * BN + c4;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int z = 0; z < p.ksplit; ++z) {
-    const float4 t = __ldcg(reinterpret_cast<const float4*>(p.slots + (static_cast<size_t>(z) * tiles_all + tile_lin) * slot_floats + in_slot));
+    const float4 t = __ldcg(reinterpret_cast<const float4*>(p.slots + (static_cast<size_t>(z) * p.n_tail + tail) * slot_floats + in_slot));
     acc.x += t.x;
     acc.y += t.y;
     acc.z += t.z;
@@ -927,7 +942,16 @@ cudaError_t launch_gemm_nn(const GemmParams& p, const GemmMaps& tm, cudaStream_t
   q.pstages = Cfg<NN>::kPStages;
   if (q.ksplit < 1) q.ksplit = 1;
   if (!PAIR) {
-    dim3 grid(n_tiles, cdiv(p.M, BM * p.mt), q.ksplit);
+    const int n_y = q.swap ? 1 : cdiv(p.M, BM * p.mt), total = n_tiles * n_y;
+    q.n_x = n_tiles;
+    if (q.ksplit == 1) {
+      q.full_tiles = total;
+      q.n_tail = 0;
+    } else if (q.n_tail <= 0) {  // every tile sliced (the caller sets n_tail to slice the last wave only)
+      q.full_tiles = 0;
+      q.n_tail = total;
+    }
+    dim3 grid(q.full_tiles + q.n_tail * q.ksplit, 1, 1);
     return launch_pdl(gemm_w4a16_kernel<NN, false>, grid, dim3(Cfg<NN>::kThreads), Cfg<NN>::smem(p.mt), stream, q, tm);
   }
   cudaLaunchConfig_t cfg = {};
@@ -990,6 +1014,7 @@ inline size_t counters_end(int OC_total, int n_members) {
 // K slices of a group GEMM with few tiles (up to 128 tokens): planned for 148 SMs so that the workspace size does not
 // depend on the device.
 constexpr int kPlanSms = 148;
+constexpr int kMaxTailSlots = 64;   // tiles x slices of a sliced last wave (256 KB of fp32 each for a 256 x 256 tile)
 inline int main_ksplit(int tiles, int nk, int sms) {
   if (tiles * 2 > sms) return 1;
   return std::max(1, std::min({8, sms / tiles, nk / 8}));
@@ -1005,7 +1030,8 @@ inline size_t main_slot_bytes_bound(int M, int IC, int OC_total, int n_members) 
 }
 
 size_t gemm_workspace_bytes(int M, int IC, int OC_total, int rank, int n_members) {
-  const size_t slots = std::max(rank > 0 ? r_slot_bytes(M, IC, rank) : 0, main_slot_bytes_bound(M, IC, OC_total, n_members));
+  size_t slots = std::max(rank > 0 ? r_slot_bytes(M, IC, rank) : 0, main_slot_bytes_bound(M, IC, OC_total, n_members));
+  if (M > 2 * BM) slots = std::max(slots, static_cast<size_t>(kMaxTailSlots) * 2 * 2 * BM * BN * 4);  // sliced last wave
   if (slots == 0) return kWsHeaderBytes;
   return counters_end(OC_total, n_members) + slots + 256;
 }
@@ -1098,8 +1124,18 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     double best = -1.0;
+    static const int env_ks0 = [] { const char* e = std::getenv("GLOWQ_GEMM_KSPLIT"); return e ? std::atoi(e) : -1; }();
+    const bool can_slice_tail = !any_separate && g.M > 2 * BM && env_ks0 != 0;
     auto consider = [&](int cnn, int cmt, bool cpair, long ctas, double reuse) {
-      const double wave_eff = static_cast<double>(ctas) / (static_cast<double>(cdiv(static_cast<int>(ctas), sms)) * sms);
+      // waves this many tiles take; a last wave that fills at most half of the SMs is K-sliced (see the work partition
+      // below) and then costs 1/slices of a wave plus the slot traffic
+      double waves = static_cast<double>(cdiv(static_cast<int>(ctas), sms));
+      const int rest = static_cast<int>(ctas % sms);
+      if (can_slice_tail && !cpair && ctas > sms && rest > 0 && rest * 2 <= sms) {
+        const int ks = std::min({8, kMaxTailSlots / rest, cdiv(g.IC, BK) / 8});
+        if (ks >= 2) waves = static_cast<double>(ctas / sms) + 1.0 / ks + 0.3;
+      }
+      const double wave_eff = static_cast<double>(ctas) / (waves * sms);
       if (wave_eff * reuse > best) {
         best = wave_eff * reuse;
         nn = cnn;
@@ -1120,7 +1156,7 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
         if (swap)
           consider(cnn, 1, false, tiles, cnn == 2 ? 1.0 : 0.9);
         else
-          consider(cnn, cmt, false, tiles * cdiv(g.M, BM * cmt), (cnn == 2 ? 1.0 : 0.8) * (cmt == 2 ? 1.0 : 0.65));
+          consider(cnn, cmt, false, tiles * cdiv(g.M, BM * cmt), (cnn == 2 ? 1.0 : 0.75) * (cmt == 2 ? 1.0 : 0.65));
       }
   }
   static const int env_ks = [] { const char* e = std::getenv("GLOWQ_GEMM_KSPLIT"); return e ? std::atoi(e) : -1; }();
@@ -1234,11 +1270,39 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
     d.tile_begin = tile_begin;
     tile_begin += cdiv(m.OC, BN * nn * (pair ? 2 : 1));
   }
+  // Work partition (see GemmParams): all tiles sliced for few tokens; for a large launch whose last wave would leave
+  // more than half of the SMs idle, only that wave's tiles are sliced, so that it takes 1/ksplit of a tile's time.
+  p.n_x = tile_begin;
+  {
+    const int total = tile_begin * cdiv(g.M, BM * mt);
+    if (p.ksplit > 1) {
+      p.full_tiles = 0;
+      p.n_tail = total;
+    } else if (!pair && !swap && !any_separate && g.M > 2 * BM && env_ks != 0) {
+      int sms = kPlanSms, dev = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      const int waves = total / sms, rest = total % sms;
+      if (waves >= 1 && rest > 0 && rest * 2 <= sms) {
+        const int ks = std::min({8, kMaxTailSlots / rest, cdiv(g.IC, BK) / 8});
+        int oc_total = 0;
+        for (int i = 0; i < g.n_members; ++i) oc_total += g.members[i].OC;
+        const size_t need = static_cast<size_t>(ks) * rest * nn * mt * BM * BN * 4;
+        const size_t off = g.workspace_bytes >= need ? ((g.workspace_bytes - need) & ~static_cast<size_t>(255)) : 0;
+        if (ks >= 2 && off >= counters_end(oc_total, g.n_members)) {
+          p.ksplit = ks;
+          p.full_tiles = waves * sms;
+          p.n_tail = rest;
+          p.slot_rows = BM;
+          p.slots = reinterpret_cast<float*>(static_cast<unsigned char*>(g.workspace) + off);
+        }
+      }
+    }
+  }
   cudaError_t e = launch_gemm(p, tm, nn, pair, stream);
   if (e == cudaSuccess && p.ksplit > 1) {
-    const int m_tiles = cdiv(g.M, BM);
-    const int n = m_tiles * tile_begin * nn * p.slot_rows * (BN / 4);
-    e = launch_pdl(slot_sum_members_kernel, dim3(cdiv(n, 256)), dim3(256), 0, stream, p, nn, tile_begin, m_tiles);
+    const int n = p.n_tail * nn * p.mt * p.slot_rows * (BN / 4);
+    e = launch_pdl(slot_sum_members_kernel, dim3(cdiv(n, 256)), dim3(256), 0, stream, p, nn);
   }
   if (e != cudaSuccess) {
     *cuda_err = e;
