@@ -421,6 +421,27 @@ def test_toy_model_through_wrappers_matches_reference(golden_toy, monkeypatch):
 
 
 @pytest.mark.gpu
+def test_gemm_with_a_sliced_last_wave():
+    """160 tiles of 256 x 256 on 148 SMs: one whole wave, and a last wave of 12 tiles that is cut into K slices whose
+    fp32 partial tiles are added by the slot-sum kernel (bias and correction included)."""
+    M, oc, ic, rank = 2560, 4096, 1024, 64
+    rng = np.random.default_rng(7)
+    lin = Linear(rng, oc, ic, rank=rank, bias=True)
+    x = rng.standard_normal((M, ic)).astype(np.float16)
+    R = (rng.standard_normal((rank, ic)) * 0.01).astype(np.float16)
+    for r_mode in (K.R_NONE, K.R_COMPUTE):
+        out = new_out(M, lin)
+        if r_mode == K.R_NONE:
+            g = make_group(dev(x), [lin], [out], kernel=K.KERNEL_GEMM)
+        else:
+            r_buf = torch.zeros(M, rank, dtype=torch.float16, device="cuda")
+            g = make_group(dev(x), [lin], [out], R_d=dev(R), r_buf=r_buf, r_mode=r_mode, alpha=1.0, kernel=K.KERNEL_GEMM)
+        for _ in range(2):   # the second call reuses the slots
+            assert run_group(g) == 0 and status_ok(g) == 0
+        assert_close(out, lin.oracle(x, R if r_mode != K.R_NONE else None, alpha=1.0), tag="sliced last wave")
+
+
+@pytest.mark.gpu
 def test_cta_pair_variant_in_subprocess():
     """The two-CTA (cta_group::2) GEMM variant (above 128 tokens) and the swapped-operand variant (up to 128 tokens)
     are opt-in through environment variables that the library reads once, so they are exercised in a child
