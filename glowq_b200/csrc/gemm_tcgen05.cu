@@ -98,7 +98,7 @@ struct GemmParams {
   // per accumulator) and the activation tile its N side (nt = 32, 64 or 128 token rows, B operand): the activation
   // tile written and re-read per K step shrinks from 128 rows to nt, which is what bounds small token counts.
   int swap, nt;
-  int debug;         // tuning experiments only (0 in production): 16 no copies after the first ring round, 32 no MMA, 64 no dequant
+  int debug;         // used by the clock trace of -DGLOWQ_GEMM_TRACE builds only (bit 2048, bit 4096 = trace CTA 1)
   // Work items (blockIdx.x, single-CTA kernels): tiles [0, full_tiles) are computed whole; each of the n_tail tiles
   // after them is cut into ksplit K slices (item = full_tiles + tail index * ksplit + slice).  Tiles are numbered
   // token tile major, column tile minor (n_x column tiles).  full_tiles = 0 slices every tile (few tokens);
@@ -123,17 +123,8 @@ __device__ __forceinline__ void g_mbar_arrive(uint32_t a) {
 __device__ __forceinline__ void g_mbar_expect_tx(uint32_t a, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool g_mbar_wait(uint32_t a, uint32_t parity, volatile int* abort_flag, uint32_t* status,
-                                            int spin_first = 0) {
+__device__ __forceinline__ bool g_mbar_wait(uint32_t a, uint32_t parity, volatile int* abort_flag, uint32_t* status) {
   uint32_t spins = 0;
-  for (int i = 0; i < spin_first; ++i) {  // non-suspending polls first: a wait that is about to succeed stays awake
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok)
-                 : "r"(a), "r"(parity)
-                 : "memory");
-    if (ok) return true;
-  }
   for (;;) {
     uint32_t ok;
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
@@ -327,7 +318,7 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
   const int m0 = PAIR ? by * (2 * BM) + static_cast<int>(crank) * BM : (p.swap ? by * p.nt : by * (BM * p.mt));
   const int n_mt = (!PAIR && p.mt == 2 && m0 + BM < p.M) ? 2 : 1;
   const int n_nt = PAIR ? 2 : ((NN == 2 && n0 + BN < mb.OC) ? 2 : 1);
-  const int nk_all = (p.debug & 1024) ? (p.nk1 + mb.nk2) / 4 : p.nk1 + mb.nk2;
+  const int nk_all = p.nk1 + mb.nk2;
   const int it0 = ks > 1 ? static_cast<int>(static_cast<long long>(nk_all) * zslice / ks) : 0;
   const int nk = ks > 1 ? static_cast<int>(static_cast<long long>(nk_all) * (zslice + 1) / ks) : nk_all;
   const int nk_packed = p.w4 ? min(nk, p.nk1) : it0;  // steps [it0, nk_packed) dequantise a packed tile
@@ -409,16 +400,12 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         const bool phase1 = it < p.nk1;
         const int kk = phase1 ? it : it - p.nk1;
         const bool packed = it < nk_packed;
-        if ((p.debug & 16) && it - it0 >= kStagesG) {
-          g_mbar_arrive(bar);
-        } else {
-          g_mbar_expect_tx(bar, (p.swap ? p.nt * (BK * 2) : n_mt * kABytes) + (packed ? 0 : NN * kBBytes));
-          const CUtensorMap* ta = phase1 ? &tm.a1 : &tm.a2;
-          g_tma_2d(sbase, ta, kk * BK, m0, bar);
-          if (n_mt == 2) g_tma_2d(sbase + kABytes, ta, kk * BK, m0 + BM, bar);
-          if (!packed)  // one box of 128 NN rows x 128 B, swizzled: NN consecutive 16 KB operand tiles
-            g_tma_2d(sbase + kBOff, phase1 ? &tm.b1[mi] : &tm.b2[mi], kk * BK, n0, bar);
-        }
+        g_mbar_expect_tx(bar, (p.swap ? p.nt * (BK * 2) : n_mt * kABytes) + (packed ? 0 : NN * kBBytes));
+        const CUtensorMap* ta = phase1 ? &tm.a1 : &tm.a2;
+        g_tma_2d(sbase, ta, kk * BK, m0, bar);
+        if (n_mt == 2) g_tma_2d(sbase + kABytes, ta, kk * BK, m0 + BM, bar);
+        if (!packed)  // one box of 128 NN rows x 128 B, swizzled: NN consecutive 16 KB operand tiles
+          g_tma_2d(sbase + kBOff, phase1 ? &tm.b1[mi] : &tm.b2[mi], kk * BK, n0, bar);
         ++issued;
         if (++st == static_cast<uint32_t>(kStagesG)) {
           st = 0;
@@ -439,12 +426,8 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       for (int it = it0; it < nk_packed; ++it) {
         if (!(ok = g_mbar_wait(pempty_b + 8 * sp, pph ^ 1, abort_flag, p.status))) break;
         const uint32_t bar = pfull_b + 8 * sp;
-        if ((p.debug & 16) && it - it0 >= kPStagesG) {
-          g_mbar_arrive(bar);
-        } else {
-          g_mbar_expect_tx(bar, kPStage);
-          g_tma_2d(pring + sp * kPStage, &tm.b1[mi], it * (BK / 8), n0, bar);  // one box of 128 NN rows x 32 B
-        }
+        g_mbar_expect_tx(bar, kPStage);
+        g_tma_2d(pring + sp * kPStage, &tm.b1[mi], it * (BK / 8), n0, bar);  // one box of 128 NN rows x 32 B
         ++issued;
         if (++sp == static_cast<uint32_t>(kPStagesG)) {
           sp = 0;
@@ -466,7 +449,6 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
       uint32_t desc_lo = static_cast<uint32_t>(desc0);
       const uint32_t desc_lo0 = desc_lo;
       const uint32_t stage16 = kStageG >> 4, boff16 = kBOff >> 4;
-      const bool skip_mma = (p.debug & 32) != 0;
       const uint32_t peer_empty = PAIR ? map_to_cta(empty_b, 1) : 0u, peer_accum = PAIR ? map_to_cta(accum_b, 1) : 0u;
       for (int it = it0; it < nk; ++it) {
         if (PAIR) {  // `bready`: the dequant warps of both CTAs and the landing of the peer's operand copies
@@ -478,7 +460,7 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           if (ok && !g_mbar_try_once(bready_b + 8 * st, ph)) ok = g_mbar_wait(bready_b + 8 * st, ph, abort_flag, p.status);
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok && !(skip_mma && it > it0)) {
+        if (ok) {
           const bool phase2 = it >= p.nk1;
           const uint32_t lr_off = (phase2 && mb.lr_separate) ? BN : 0;
           const bool first = phase2 ? (mb.lr_separate && it == p.nk1) : (it == it0);
@@ -629,7 +611,7 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
 #pragma unroll
           for (int h = 0; h < H; ++h) fetch_sz(h, (it + H) >> 1, nx_s[h], nx_z[h]);
         }
-        if (ok && !(p.debug & 64)) {
+        if (ok) {
           const uint32_t sbase = ring + st * kStageG, psrc = pring + sp * kPStage;
 #pragma unroll
           for (int h = 0; h < H; ++h) {
