@@ -1007,7 +1007,8 @@ inline size_t main_slot_bytes_bound(int M, int IC, int OC_total, int n_members) 
   const int m_tiles = cdiv(M, BM);
   if (M <= 16 || M > 2 * BM || cdiv(OC_total, 2 * BN) * m_tiles * 2 > kPlanSms) return 0;
   const int tiles_ub = (cdiv(OC_total, BN) + n_members) * m_tiles;  // 128 x 128 tiles
-  const int slots_ub = std::min(8 * tiles_ub, kPlanSms + tiles_ub);
+  // at most 8 slices, and slices x (256-column tiles) <= SMs, i.e. at most 2 SMs' worth of 128-column slot tiles
+  const int slots_ub = std::min(8 * tiles_ub, 2 * kPlanSms + tiles_ub);
   return static_cast<size_t>(slots_ub) * slot_rows_for(M) * BN * 4;
 }
 
