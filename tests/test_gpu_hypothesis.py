@@ -48,3 +48,32 @@ def test_forward_parity_random_layouts(oc, ic8, M, rank8, bias, gs, seed):
     assert np.isfinite(got).all()
     ma, mr = O.parity_errors(got, want)
     assert ma <= 2e-2 and (mr <= 1e-3 or ma <= 2e-3), (ma, mr)
+
+
+@settings(max_examples=20, deadline=None, suppress_health_check=[HealthCheck.too_slow, HealthCheck.data_too_large])
+@given(M=st.integers(17, 600), ocs=st.lists(st.integers(8, 700), min_size=1, max_size=3), ic64=st.integers(2, 40),
+       rank8=st.sampled_from([0, 2, 8, 16]), alpha=st.sampled_from([1.0, 1.0, 0.5]), bias=st.booleans(),
+       seed=st.integers(0, 2**16))
+def test_group_parity_through_the_automatic_kernel_choice(M, ocs, ic64, rank8, alpha, bias, seed):
+    """17..600 tokens take the tensor-core GEMM: K-sliced launches (few tiles), one or two token tiles, the separate
+    correction accumulator (alpha != 1), ragged output widths, several members in one launch - with a workspace of
+    exactly the size the library asks for."""
+    ic, rank = ic64 * 64, rank8 * 8
+    rng = np.random.default_rng(seed)
+    lins = [Linear(rng, oc, ic, 128, bias=bias, rank=rank) for oc in ocs]
+    x = rng.standard_normal((M, ic)).astype(np.float16)
+    outs = [new_out(M, lin) for lin in lins]
+    if rank:
+        R = (rng.standard_normal((rank, ic)) * 0.01).astype(np.float16)
+        r_buf = torch.zeros(M, rank, dtype=torch.float16, device="cuda")
+        g = make_group(dev(x), lins, outs, R_d=dev(R), r_buf=r_buf, r_mode=K.R_COMPUTE, alpha=alpha)
+    else:
+        R = None
+        g = make_group(dev(x), lins, outs)
+    for _ in range(2):   # the second call reuses slots and counters
+        assert run_group(g) == 0 and status_ok(g) == 0
+    for lin, out in zip(lins, outs):
+        got = out.float().cpu().numpy()
+        assert np.isfinite(got).all()
+        ma, mr = O.parity_errors(got, lin.oracle(x, R, alpha=alpha) if rank else lin.oracle(x))
+        assert ma <= 2e-2 and (mr <= 1e-3 or ma <= 2e-3), (ma, mr)
