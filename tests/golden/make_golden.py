@@ -2,7 +2,7 @@
 
 Run where the reference checkout is available:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/GLOWQ        (or GLOWQ_REFERENCE=/path/to/GLOWQ)
 
 It imports the reference in place (nothing is copied), runs its quantiser, its pure-torch
 dequantiser, its replacement module and its correction wrapper / patchers on seeded CPU
@@ -14,7 +14,9 @@ import os
 import sys
 import types
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("GLOWQ_REFERENCE", "")
+if not os.path.isdir(os.path.join(REF, "src", "cuda_w4a16")):
+    sys.exit("usage: make_golden.py /path/to/GLOWQ  (a checkout of the reference with src/cuda_w4a16)")
 HERE = os.path.dirname(os.path.abspath(__file__))
 os.environ.update(DISABLE_TRITON="1", W4A16_FORCE_GEMM="1", W4A16_GEMM_CUDA="0")
 sys.path.insert(0, os.path.join(REF, "src"))
