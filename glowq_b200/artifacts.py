@@ -103,8 +103,12 @@ def load_packed(model: nn.Module, path: str, device=None, strict: bool = True):
         for b in _BUFFERS:
             t = tensors[f"{name}.{b}"]
             buf = getattr(new, b)
-            if tuple(buf.shape) != tuple(t.shape) or buf.dtype != t.dtype:
-                raise ValueError(f"{name}.{b}: stored {tuple(t.shape)} {t.dtype}, expected {tuple(buf.shape)} {buf.dtype}")
+            # the stored tensors have the quantiser's shapes (columns padded to whole groups, as from_float leaves
+            # them), which may be wider than the fresh shell's ceil(IC/8) columns
+            if (buf.dtype != t.dtype or t.dim() != 2 or t.size(0) != buf.size(0) or t.size(1) < buf.size(1)):
+                raise ValueError(f"{name}.{b}: stored {tuple(t.shape)} {t.dtype}, expected at least "
+                                 f"{tuple(buf.shape)} {buf.dtype}")
+            buf.resize_(t.shape)
             buf.copy_(t)
         if meta["bias"]:
             new.bias.data.copy_(tensors[f"{name}.bias"])

@@ -52,6 +52,7 @@ struct DeviceInfo {
   int sms = 0;
 };
 DeviceInfo g_dev[64];
+std::mutex g_dev_mutex;
 
 int device_info(const DeviceInfo** out) {
   int dev = 0;
@@ -59,6 +60,7 @@ int device_info(const DeviceInfo** out) {
   if (e != cudaSuccess) return fail_cuda(e);
   if (dev < 0 || dev >= 64) return GLOWQ_ERR_UNSUPPORTED_DEVICE;
   DeviceInfo& d = g_dev[dev];
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
   if (!d.probed) {
     if ((e = cudaDeviceGetAttribute(&d.major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess) return fail_cuda(e);
     if ((e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return fail_cuda(e);
@@ -240,6 +242,12 @@ int validate_group(const glowq_w4a16_group_t& g) {
   if (g.group_size <= 0 || g.group_size % 8 != 0) return GLOWQ_ERR_BAD_GROUP_SIZE;
   if (g.x_stride < g.IC) return GLOWQ_ERR_BAD_STRIDE;
   if (g.out_dtype != GLOWQ_OUT_F16 && g.out_dtype != GLOWQ_OUT_F32) return GLOWQ_ERR_BAD_ARGUMENT;
+#if !defined(GLOWQ_GEMV_TRACE) && !defined(GLOWQ_GEMM_TRACE)
+  // reserved fields must be zero: a struct that was not cleared is refused instead of steering anything
+  if (g.reserved != 0) return GLOWQ_ERR_BAD_ARGUMENT;
+  for (int i = 0; i < g.n_members; ++i)
+    if (g.members[i].reserved != 0) return GLOWQ_ERR_BAD_ARGUMENT;
+#endif
   if (g.r_mode != GLOWQ_R_NONE && g.r_mode != GLOWQ_R_COMPUTE && g.r_mode != GLOWQ_R_LOAD) return GLOWQ_ERR_BAD_ARGUMENT;
   if (g.r_mode != GLOWQ_R_NONE) {
     if (g.rank <= 0 || !g.r_buf) return GLOWQ_ERR_BAD_ARGUMENT;
@@ -560,8 +568,12 @@ int glowq_w4a16_gemv_forward_static(const void* x, const int32_t* qweight, const
   if (rc != GLOWQ_OK) return rc;
   if (M == 0) return GLOWQ_OK;
   // Counters must start at zero whatever an earlier (possibly failed) call left behind; partial sums are
-  // always written before they are read and need no clearing.
-  cudaError_t e = cudaMemsetAsync(scratch, 0, pl.off_r_partial, static_cast<cudaStream_t>(stream));
+  // always written before they are read and need no clearing.  The status word is left alone: it keeps a
+  // timeout of an earlier call until glowq_w4a16_read_status(NULL, stream) collects it.
+  unsigned char* sc = static_cast<unsigned char*>(scratch);
+  cudaError_t e = cudaMemsetAsync(sc, 0, WS_STATUS * 4, static_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess)
+    e = cudaMemsetAsync(sc + (WS_STATUS + 1) * 4, 0, pl.off_r_partial - (WS_STATUS + 1) * 4, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail_cuda(e);
   glowq_w4a16_group_t g;
   fill_plain(g, x, qweight, scales, qzeros, out, M, IC, OC, group_size, weight_stride_i32, zero_stride_i32, scale_stride,
@@ -596,7 +608,10 @@ int glowq_w4a16_group_forward_host(const glowq_w4a16_group_t* group, const void*
 }
 
 int glowq_w4a16_read_status(void* workspace, void* stream) {
-  if (!workspace) return GLOWQ_ERR_BAD_ARGUMENT;
+  if (!workspace) {  // the library-resident scratch of glowq_w4a16_gemv_forward_static on the current device
+    const int rc = static_scratch_address(&workspace);
+    if (rc != GLOWQ_OK) return rc;
+  }
   uint32_t host = 0;
   uint32_t* word = static_cast<uint32_t*>(workspace) + WS_STATUS;
   cudaStream_t s = static_cast<cudaStream_t>(stream);

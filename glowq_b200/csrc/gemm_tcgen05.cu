@@ -463,7 +463,9 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
         if (ok) {
           const bool phase2 = it >= p.nk1;
           const uint32_t lr_off = (phase2 && mb.lr_separate) ? BN : 0;
-          const bool first = phase2 ? (mb.lr_separate && it == p.nk1) : (it == it0);
+          // the first MMA into an accumulator overwrites it: the slice's first step (which may lie in the correction
+          // phase when K is sliced), and the first correction step when the correction has an accumulator of its own
+          const bool first = (it == it0) || (phase2 && mb.lr_separate && it == p.nk1);
           if (!PAIR && p.swap) {
             // accumulator nn: 128 output columns (TMEM lanes) x nt tokens (TMEM columns nn * nt ..)
             const uint32_t idesc = (1u << 4) | ((static_cast<uint32_t>(p.nt) >> 3) << 17) | ((BM >> 4) << 24);
@@ -663,6 +665,9 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
     // ---- epilogue: this warp owns TMEM lanes 32 (warp % 4) .. +31 = 32 tokens; one token per lane
     ok = ok && g_mbar_wait(accum_b, 0, abort_flag, p.status);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // With a separate correction accumulator, a K slice that lies wholly in one phase never writes the other
+    // phase's accumulator: that one counts as zero.
+    const bool has_main = it0 < p.nk1, has_lr = nk > p.nk1;
     const int q = warp & 3;                          // TMEM lane quadrant this warp may read
     constexpr int kWays = Cfg<NN>::kDequantWarps / 4;  // warps that share a lane quadrant split the tile's columns
     constexpr int kCbPer = (BN / 32) / kWays;
@@ -727,8 +732,8 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           for (int j = 0; j < 32; ++j) {
             const int tok = m0 + cb * 32 + j;
             if (tok < p.M) {
-              float v = __uint_as_float(acc[j]);
-              if (NN == 1 && mb.lr_separate) v = fmaf(mb.alpha, __uint_as_float(lr[j]), v);
+              float v = (has_main || !mb.lr_separate) ? __uint_as_float(acc[j]) : 0.f;
+              if (NN == 1 && mb.lr_separate && has_lr) v = fmaf(mb.alpha, __uint_as_float(lr[j]), v);
               v += bias;
               const size_t idx = static_cast<size_t>(tok) * mb.out_stride + col;
               if (p.out_fp32)
@@ -777,8 +782,8 @@ gemm_w4a16_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ 
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            v[j] = __uint_as_float(acc[j]);
-            if (NN == 1 && mb.lr_separate) v[j] = fmaf(mb.alpha, __uint_as_float(lr[j]), v[j]);
+            v[j] = (has_main || !mb.lr_separate) ? __uint_as_float(acc[j]) : 0.f;
+            if (NN == 1 && mb.lr_separate && has_lr) v[j] = fmaf(mb.alpha, __uint_as_float(lr[j]), v[j]);
           }
           if (ks > 1) {
             float* sl = p.slots + (static_cast<size_t>(zslice) * p.n_tail + (tile_lin - p.full_tiles)) * kSlotFloats +

@@ -71,6 +71,17 @@ __device__ __forceinline__ void cp_async_mbar_arrive(uint64_t* b) {
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
 
+// Tuning switches (skip the MMAs, skip the copies, other wait flavours, timeline) exist only in builds with
+// -DGLOWQ_GEMV_TRACE; otherwise this is the constant 0 and every branch on it is compiled out.
+__device__ __forceinline__ int tuning_bits(const GemvParams& p) {
+#ifdef GLOWQ_GEMV_TRACE
+  return p.debug;
+#else
+  (void)p;
+  return 0;
+#endif
+}
+
 struct Ctx {
   volatile int* abort_flag;
   uint32_t* status;
@@ -81,7 +92,7 @@ struct Ctx {
 // CTA b -> %globaltimer at workspace + 32 MB.
 __device__ __forceinline__ void trace_event(const GemvParams& p, int e) {
 #ifdef GLOWQ_GEMV_TRACE
-  if (p.debug & 16) {
+  if (tuning_bits(p) & 16) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(p.ws_head) + (32u << 20))[blockIdx.x * 16 + e] = t;
@@ -401,7 +412,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   }
   __syncthreads();
   if (threadIdx.x == 0) trace_event(p, 1);
-  Ctx cx{&s_abort, p.ws_head + WS_STATUS, p.debug};
+  Ctx cx{&s_abort, p.ws_head + WS_STATUS, tuning_bits(p)};
   const uint32_t full_u32 = smem_u32(full_bar), empty_u32 = smem_u32(empty_bar);
   const uint32_t mfull_u32 = smem_u32(meta_full), mempty_u32 = smem_u32(meta_empty);
   const uint32_t rempty_u32 = smem_u32(red_empty);
@@ -417,7 +428,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       for (int c = 0; c < n_chunks; ++c) {
         if (!(ok = mbar_wait_u32(empty_u32 + st * 8, ph ^ 1, cx))) break;
         if (lane == 0) {
-          if (p.debug & 2) {
+          if (tuning_bits(p) & 2) {
             mbar_arrive(full_bar + st);
           } else {
             mbar_arrive_expect_tx(full_bar + st, kStageBytes);
@@ -446,7 +457,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
         }
       }
     }
-    if (!ok && !(p.debug & 2)) {
+    if (!ok && !(tuning_bits(p) & 2)) {
       // Draining: copies already issued still land in this CTA's shared memory; wait (bounded) for them so that
       // the CTA does not retire under an in-flight copy.
       for (uint32_t j = (issued > static_cast<uint32_t>(S) ? issued - S : 0); j < issued; ++j) {
@@ -633,7 +644,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
         ok = ok && mbar_wait_u32(full_u32 + st * 8, ph, cx);
         if (threadIdx.x == 0 && k == 0 && c == 0) trace_event(p, 4);
         const int gl = c * kChunkGroups + warp;
-        if (ok && gl < ng && !(p.debug & 1)) {
+        if (ok && gl < ng && !(tuning_bits(p) & 1)) {
           const uint32_t wbase = ring_lane + st * kStageBytes;
           uint4 W[RT][2];
 #pragma unroll

@@ -6,6 +6,8 @@ Differences from the reference, all on the host side of the same interface:
 * forward runs only on CUDA tensors of an sm_100 device; there is no pure-torch or CPU path;
 * the kernel choice knobs W4A16_KERNEL_OUT_DTYPE / W4A16_GEMV_M_MAX / W4A16_FORCE_GEMM / W4A16_FORCE_GEMV are
   read once when the module is built (the reference re-reads the environment on every call, linear.py:172-177);
+  W4A16_GEMV_M_MAX has no built-in default of 128 here: unset, the library switches kernels where it measured the
+  cross-over (16 tokens);
   the dequant-cache / chunk / JIT knobs belong to fallbacks that do not exist here;
 * output and scratch buffers are caller-side torch tensors; the library allocates nothing.
 """
@@ -112,10 +114,12 @@ class CudaW4A16Linear(nn.Module):
         self.bias = nn.Parameter(torch.empty(self.out_features, dtype=torch.float16)) if bias else None
 
         self._ext = None
-        self._gemv_threshold = _env_int("W4A16_GEMV_M_MAX", "CUDA_MIXED_GEMV_M_MAX", default=128)
+        # -1: the knob is unset and the library's own switch-over applies
+        self._gemv_threshold = _env_int("W4A16_GEMV_M_MAX", "CUDA_MIXED_GEMV_M_MAX", default=-1)
         self._force_gemm = _env_flag("W4A16_FORCE_GEMM", "CUDA_MIXED_FORCE_GEMM")
         self._force_gemv = _env_flag("W4A16_FORCE_GEMV", "CUDA_MIXED_FORCE_GEMV") or _env_flag("W4A16_USE_GEMV")
         self._out_dtype = _get_kernel_out_dtype()
+        self._check_status = _env_flag("GLOWQ_CHECK_STATUS")
         self._ws: Optional[torch.Tensor] = None      # scratch for plain (uncorrected) calls
         self._ws_key = None
 
@@ -130,12 +134,15 @@ class CudaW4A16Linear(nn.Module):
         return self._ext
 
     def kernel_choice(self, m: int) -> int:
-        """Which kernel a call with ``m`` tokens asks for.  The library's own switch-over (weight-streaming
-        kernel up to 16 tokens, tensor-core kernel above) applies unless a FORCE knob is set."""
+        """Which kernel a call with ``m`` tokens asks for (linear.py:172-181): a FORCE knob wins; otherwise an
+        explicitly set W4A16_GEMV_M_MAX sends ``m <= W4A16_GEMV_M_MAX`` to the weight-streaming kernel and anything
+        larger to the tensor-core kernel; with the knob unset the library's own switch-over (16 tokens) applies."""
         if self._force_gemm:
             return K.KERNEL_GEMM
         if self._force_gemv:
             return K.KERNEL_GEMV
+        if self._gemv_threshold >= 0:
+            return K.KERNEL_GEMV if m <= self._gemv_threshold else K.KERNEL_GEMM
         return K.KERNEL_AUTO
 
     def _flatten_input(self, x: torch.Tensor):
@@ -200,6 +207,8 @@ class CudaW4A16Linear(nn.Module):
             grp.workspace, grp.workspace_bytes = ws.data_ptr(), ws.numel()
             grp.stream = torch.cuda.current_stream(x2d.device).cuda_stream
             ext.check(ext.lib.glowq_w4a16_group_forward(grp), "glowq_w4a16_group_forward")
+            if self._check_status:   # debugging aid: synchronises the stream after every launch
+                ext.check(ext.lib.glowq_w4a16_read_status(grp.workspace, grp.stream), "device status")
         return out
 
     # ------------------------------------------------------------------ reference-named entry points

@@ -59,6 +59,34 @@ class QLinear:
         self.bias = (torch.randn(oc, generator=gen, device=device) * 0.1).to(torch.float16) if bias else None
         self.L = (torch.randn(oc, rank, generator=gen, device=device) * 0.01).to(torch.float16) if rank else None
 
+    def as_module(self):
+        """A ``CudaW4A16Linear`` shell over the same packed tensors (what ``glowq_b200.tp`` shards)."""
+        from .cuda_w4a16.linear import CudaW4A16Linear
+        mod = CudaW4A16Linear(self.ic, self.oc, self.group_size, bias=self.bias is not None).to(self.qweight.device)
+        for name, t in (("qweight_i32", self.qweight), ("qzeros_i32", self.qzeros), ("scales_f16", self.scales)):
+            buf = getattr(mod, name)
+            buf.resize_(t.shape)
+            buf.copy_(t)
+        if self.bias is not None:
+            mod.bias.data.copy_(self.bias)
+        return mod
+
+    @classmethod
+    def from_module(cls, mod, L):
+        """The other direction: a (sharded) module and its left factor as a ``QLinear``."""
+        q = cls.__new__(cls)
+        q.qweight, q.qzeros, q.scales = (mod.qweight_i32.contiguous(), mod.qzeros_i32.contiguous(),
+                                         mod.scales_f16.contiguous())
+        q.oc, q.ic, q.group_size = mod.out_features, mod.in_features, mod.group_size
+        q.bias = None if mod.bias is None else mod.bias.data.contiguous()
+        q.L = None if L is None else L.contiguous()
+        return q
+
+    def numpy_parts(self):
+        return {"qweight": self.qweight.cpu().numpy(), "qzeros": self.qzeros.cpu().numpy(),
+                "scales": self.scales.cpu().numpy(), "L": None if self.L is None else self.L.cpu().numpy(),
+                "bias": None if self.bias is None else self.bias.cpu().numpy()}
+
     def weight_bytes(self, corrected: bool) -> int:
         n = self.qweight.numel() * 4 + self.scales.numel() * 2 + self.qzeros.numel() * 4
         if self.bias is not None:
@@ -82,39 +110,64 @@ class GroupSpec:
 
 
 class LinearStack:
+    """``tp_world`` > 1: every rank draws the SAME full model from ``seed`` and keeps its tensor-parallel shard, cut by
+    ``glowq_b200.tp``: q/k/v and gate/up by output rows (whole heads / whole 128-row blocks, R replicated), o_proj and
+    down_proj by input columns at quantisation-group boundaries (R cut with them, L replicated).  The partial outputs
+    of the row-split members add up to the unsharded result; ``tp_reference`` keeps layer 0's unsharded o_proj and
+    down_proj (numpy) so that a caller can check that sum."""
+
     def __init__(self, shape: StackShape, device="cuda", seed: int = 0, layers: Optional[int] = None,
                  enabled_groups: Optional[set] = None, tp_rank: int = 0, tp_world: int = 1):
+        from . import tp as TP
         self.shape, self.device = shape, torch.device(device)
         self.ext = K.load_w4a16_extension()
         self.tp_rank, self.tp_world = tp_rank, tp_world
-        gen = torch.Generator(device=self.device).manual_seed(seed + 1000 * tp_rank)
+        gen = torch.Generator(device=self.device).manual_seed(seed)     # same stream of draws on every rank
         s, r = shape, shape.rank
         n_layers = layers if layers is not None else s.layers
         tp = tp_world
-        if s.q_out % tp or s.kv_out % tp or (s.inter // 128) < tp:
+        if tp > 1 and (s.q_out % (tp * s.head_dim) or s.kv_out % (tp * s.head_dim) or (s.inter // 128) < tp
+                       or s.head_dim % 128):
             raise ValueError(f"{s.name} does not shard over {tp} ranks")
-        self.inter_local = self._row_shard_cols(s.inter, tp, tp_rank)
-        self.attn_local = s.q_out // tp
+        # input-column ranges of the row-split members on this rank (whole quantisation groups)
+        a0, a1 = [(g0 * 128, g1 * 128) for g0, g1 in TP.group_bounds(s.q_out // 128, tp)][tp_rank]
+        i0, i1 = [(g0 * 128, g1 * 128) for g0, g1 in TP.group_bounds(s.inter // 128, tp)][tp_rank]
+        self.attn_cols, self.inter_cols = (a0, a1), (i0, i1)
+        self.inter_local, self.attn_local = i1 - i0, a1 - a0
         self.groups: List[GroupSpec] = []
+        self.tp_reference: Dict[str, dict] = {}
 
         def fac(rows, cols):
             return (torch.randn(rows, cols, generator=gen, device=self.device) * 0.01).to(torch.float16)
 
+        def col_shard(full: QLinear, multiple: int) -> QLinear:
+            if tp == 1:
+                return full
+            sh, L_sh = TP.column_parallel_shard(full.as_module(), tp_rank, tp, multiple=multiple, L=full.L)
+            return QLinear.from_module(sh, L_sh)
+
+        def row_shard(full: QLinear, R: torch.Tensor, key: str, li: int):
+            if tp == 1:
+                return full, R
+            if li == 0 and tp_rank == 0:
+                self.tp_reference[key] = dict(full.numpy_parts(), R=R.cpu().numpy())
+            sh, R_sh, _ = TP.row_parallel_shard(full.as_module(), tp_rank, tp, R=R)
+            return QLinear.from_module(sh, full.L), R_sh
+
         for li in range(n_layers):
             def on(key):
                 return enabled_groups is None or key in enabled_groups
-            qkv = [QLinear(s.q_out // tp, s.hidden, r, gen, self.device, s.qkv_bias),
-                   QLinear(s.kv_out // tp, s.hidden, r, gen, self.device, s.qkv_bias),
-                   QLinear(s.kv_out // tp, s.hidden, r, gen, self.device, s.qkv_bias)]
+            qkv = [col_shard(QLinear(oc, s.hidden, r, gen, self.device, s.qkv_bias), s.head_dim)
+                   for oc in (s.q_out, s.kv_out, s.kv_out)]
             self.groups.append(GroupSpec(f"layer{li}_qkv", qkv, fac(r, s.hidden), "hidden", on(f"layer{li}_qkv")))
-            o = QLinear(s.hidden, self.attn_local, r, gen, self.device)
             k = f"model.layers.{li}.self_attn.o_proj"
-            self.groups.append(GroupSpec(k, [o], fac(r, self.attn_local), "attn", on(k)))
-            mlp = [QLinear(self.inter_local, s.hidden, r, gen, self.device) for _ in range(2)]
+            o, R_o = row_shard(QLinear(s.hidden, s.q_out, r, gen, self.device), fac(r, s.q_out), "o_proj", li)
+            self.groups.append(GroupSpec(k, [o], R_o, "attn", on(k)))
+            mlp = [col_shard(QLinear(s.inter, s.hidden, r, gen, self.device), 128) for _ in range(2)]
             self.groups.append(GroupSpec(f"layer{li}_mlp", mlp, fac(r, s.hidden), "hidden", on(f"layer{li}_mlp")))
-            d = QLinear(s.hidden, self.inter_local, r, gen, self.device)
             k = f"model.layers.{li}.mlp.down_proj"
-            self.groups.append(GroupSpec(k, [d], fac(r, self.inter_local), "inter", on(k)))
+            d, R_d = row_shard(QLinear(s.hidden, s.inter, r, gen, self.device), fac(r, s.inter), "down_proj", li)
+            self.groups.append(GroupSpec(k, [d], R_d, "inter", on(k)))
         self._plans = {}
 
     @staticmethod
@@ -156,11 +209,16 @@ class LinearStack:
         s = self.shape
         dt = torch.float16 if out_dtype == K.OUT_F16 else torch.float32
         gen = torch.Generator(device=self.device).manual_seed(2)
-        inputs = {"hidden": torch.randn(M, s.hidden, generator=gen, device=self.device).to(torch.float16),
-                  "attn": torch.randn(M, self.attn_local, generator=gen, device=self.device).to(torch.float16),
-                  "inter": torch.randn(M, self.inter_local, generator=gen, device=self.device).to(torch.float16)}
+        full = {"hidden": torch.randn(M, s.hidden, generator=gen, device=self.device).to(torch.float16),
+                "attn": torch.randn(M, s.q_out, generator=gen, device=self.device).to(torch.float16),
+                "inter": torch.randn(M, s.inter, generator=gen, device=self.device).to(torch.float16)}
+        # every rank draws the same full activations and keeps the columns its row-split members consume
+        inputs = {"hidden": full["hidden"],
+                  "attn": full["attn"][:, self.attn_cols[0]:self.attn_cols[1]].contiguous(),
+                  "inter": full["inter"][:, self.inter_cols[0]:self.inter_cols[1]].contiguous()}
         calls = []
         keep = [inputs]
+        group_outs = []
         stream = torch.cuda.current_stream(self.device).cuda_stream
         for g in self.groups:
             outs = [torch.empty(M, m.oc, dtype=dt, device=self.device) for m in g.members]
@@ -198,9 +256,10 @@ class LinearStack:
                 calls.append(c)
                 keep.append(ws)
             keep += [outs, r_buf]
+            group_outs.append(outs)
         arr = (K.Group * len(calls))(*calls)
-        plan = {"calls": arr, "n": len(calls), "inputs": inputs, "keep": keep,
-                "last_out": keep[-2][-1], "M": M}
+        plan = {"calls": arr, "n": len(calls), "inputs": inputs, "full_inputs": full, "keep": keep,
+                "last_out": keep[-2][-1], "M": M, "group_outs": group_outs}
         self._plans[key] = plan
         return plan
 

@@ -75,7 +75,7 @@ typedef struct glowq_w4a16_member {
   int32_t L_stride;
   int32_t out_stride;
   float alpha;            /* alpha_svd of this member (step3_eval_dataset.py:511)             */
-  int32_t reserved;
+  int32_t reserved;       /* must be 0                                                          */
 } glowq_w4a16_member_t;
 
 /* A group of 1..4 linears that consume the same x and share one right factor R_g. */
@@ -94,10 +94,10 @@ typedef struct glowq_w4a16_group {
   int32_t group_size;
   int32_t r_mode;
   int32_t out_dtype;      /* GLOWQ_OUT_F16 / GLOWQ_OUT_F32 (W4A16_KERNEL_OUT_DTYPE)           */
-  int32_t kernel;         /* GLOWQ_KERNEL_AUTO: streaming kernel for M <= 16 (<= 32 if small), else GEMM */
+  int32_t kernel;         /* GLOWQ_KERNEL_AUTO: streaming kernel for M <= 16, tensor-core GEMM above         */
   int32_t n_members;
   int32_t split_k;        /* 0 = choose; >0 forces the number of K slices of the GEMV         */
-  int32_t reserved;
+  int32_t reserved;       /* must be 0 (GLOWQ_ERR_BAD_ARGUMENT otherwise)                       */
   glowq_w4a16_member_t members[GLOWQ_MAX_MEMBERS];
 } glowq_w4a16_group_t;
 
@@ -193,7 +193,8 @@ int glowq_w4a16_allreduce_f16(const glowq_w4a16_peers_t* peers, void* inout, int
 size_t glowq_w4a16_workspace_bytes(int M, int IC, int OC_total, int rank, int n_members);
 
 /* Copy the device status word of a workspace to the host (synchronises `stream`) and clear it.
- * Returns GLOWQ_OK or GLOWQ_ERR_DEVICE_TIMEOUT. */
+ * Returns GLOWQ_OK or GLOWQ_ERR_DEVICE_TIMEOUT.  workspace == NULL reads the status word of the built-in
+ * scratch that glowq_w4a16_gemv_forward_static uses on the current device (that entry point never clears it). */
 int glowq_w4a16_read_status(void* workspace, void* stream);
 
 #ifdef __cplusplus

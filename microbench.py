@@ -1,6 +1,6 @@
 """Single-launch micro-benchmark of the corrected W4A16 kernels on named shapes.
 
-    python -m glowq_b200.microbench --shapes gu14b,qkv3b --M 1,8 --modes plain,corr [--kernel 0|1|2] [--iters N]
+    python microbench.py --shapes gu14b,qkv3b --M 1,8 --modes plain,corr [--kernel 0|1|2] [--iters N]
 
 Every configuration is timed as a CUDA-graph replay over enough distinct weight copies to exceed L2, with CUDA events
 on the launching stream; one JSON line per (shape, M, mode) with microseconds per launch, algorithmic GB/s (and its
@@ -11,17 +11,21 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import sys
 
 import torch
 
-from .cuda_w4a16 import kernels as K
-from .stack import QLinear
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from glowq_b200.cuda_w4a16 import kernels as K  # noqa: E402
+from glowq_b200.stack import QLinear  # noqa: E402
 
 SHAPES = {  # name: (output rows of each member, input columns, rank)
     "qkv3b": ([3072, 1024, 1024], 3072, 64), "o3b": ([3072], 3072, 64), "gu3b": ([8192, 8192], 3072, 64),
     "down3b": ([3072], 8192, 64), "k3b": ([1024], 3072, 64),
     "qkv7b": ([3584, 512, 512], 3584, 128), "gu7b": ([18944, 18944], 3584, 128), "down7b": ([3584], 18944, 128),
     "qkv13b": ([5120, 5120, 5120], 5120, 128), "gu13b": ([13824, 13824], 5120, 128), "down13b": ([5120], 13824, 128),
+    "o13b": ([5120], 5120, 128),
     "qkv14b": ([5120, 1024, 1024], 5120, 256), "o14b": ([5120], 5120, 256), "gu14b": ([17408, 17408], 5120, 256),
     "down14b": ([5120], 17408, 256), "opt_qkv": ([2048, 2048, 2048], 2048, 64),
 }
@@ -29,7 +33,7 @@ SHAPES = {  # name: (output rows of each member, input columns, rank)
 
 def measured_hbm_gbs() -> float:
     try:
-        root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+        root = os.path.dirname(os.path.abspath(__file__))
         with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
             return float(json.load(f)["hbm_gbs"])
     except Exception:  # noqa: BLE001
@@ -43,7 +47,6 @@ def main():
     ap.add_argument("--modes", default="plain,corr")
     ap.add_argument("--split-k", type=int, default=0)
     ap.add_argument("--iters", type=int, default=200)
-    ap.add_argument("--debug", type=int, default=0, help="kernel tuning switches (0 in any real measurement)")
     ap.add_argument("--kernel", type=int, default=0, help="0 auto, 1 weight-streaming kernel, 2 tensor-core GEMM")
     args = ap.parse_args()
     ext = K.load_w4a16_extension()
@@ -68,7 +71,6 @@ def main():
                     g = K.Group()
                     g.x, g.M, g.IC, g.x_stride = x.data_ptr(), M, ic, ic
                     g.group_size, g.kernel, g.split_k = 128, args.kernel, args.split_k
-                    g.reserved = args.debug
                     r_buf = torch.zeros(M, rank, dtype=torch.float16, device=dev)
                     if mode == "corr":
                         g.rank, g.r_mode, g.R, g.R_stride, g.r_buf = rank, K.R_COMPUTE, R.data_ptr(), ic, r_buf.data_ptr()

@@ -22,10 +22,26 @@ def dev(a):
 class Linear:
     """One quantised linear: numpy originals + device copies."""
 
-    def __init__(self, rng, oc, ic, gs=128, bias=False, rank=0, w_std=0.02):
+    def __init__(self, rng, oc, ic, gs=128, bias=False, rank=0, w_std=0.02, quantize=True):
         self.oc, self.ic, self.gs = oc, ic, gs
-        w = (rng.standard_normal((oc, ic)) * w_std).astype(np.float16)
-        self.qweight, self.qzeros, self.scales, self.icp = O.quantize_per_group_w4(w, gs)
+        if quantize:
+            w = (rng.standard_normal((oc, ic)) * w_std).astype(np.float16)
+            self.qweight, self.qzeros, self.scales, self.icp = O.quantize_per_group_w4(w, gs)
+        else:
+            # codes, zero-points and scales drawn directly, in the ranges RTN gives N(0, w_std) weights (no quantiser
+            # pass: seconds instead of tens of seconds for the largest shapes); unused zero nibbles hold 8 as the
+            # packer leaves them
+            assert ic % gs == 0
+            G = ic // gs
+            self.icp = ic
+            self.qweight = rng.integers(-2**31, 2**31, size=(oc, ic // 8), dtype=np.int64).astype(np.int32)
+            z = rng.integers(0, 16, size=(oc, (G + 7) // 8 * 8), dtype=np.int64)
+            z[:, G:] = 8
+            zw = np.zeros((oc, (G + 7) // 8), dtype=np.int64)
+            for j in range(8):
+                zw |= z[:, j::8] << (4 * j)
+            self.qzeros = (zw & 0xFFFFFFFF).astype(np.uint32).view(np.int32)
+            self.scales = rng.uniform(0.3 * w_std, 0.55 * w_std, size=(oc, G)).astype(np.float16)
         self.bias = (rng.standard_normal(oc) * 0.1).astype(np.float16) if bias else None
         self.L = (rng.standard_normal((oc, rank)) * 0.01).astype(np.float16) if rank else None
         self.d_qweight, self.d_qzeros, self.d_scales = dev(self.qweight), dev(self.qzeros), dev(self.scales)

@@ -49,6 +49,24 @@ def test_round_trip_equals_fresh_conversion(tmp_path, bias):
     assert isinstance(loaded.lm_head, nn.Linear)
 
 
+def test_round_trip_with_input_width_that_is_not_a_whole_number_of_groups(tmp_path):
+    """in_features = 200 with groups of 128: the quantiser pads to 256 columns (32 packed words), a fresh shell has
+    ceil(200/8) = 25; the loader must take the stored, padded tensors as from_float does."""
+    class Tiny(nn.Module):
+        def __init__(self):
+            super().__init__()
+            torch.manual_seed(5)
+            self.proj = nn.Linear(200, 16, bias=True)
+
+    src = Tiny()
+    converted = convert_to_cuda_w4a16(copy.deepcopy(src), 128)
+    assert tuple(converted.proj.qweight_i32.shape) == (16, 32)
+    path = str(tmp_path / "ragged.pt")
+    assert save_packed(converted, path) == 1
+    loaded, _, _ = load_packed(copy.deepcopy(src), path)
+    _assert_same_packed(converted, loaded)
+
+
 def test_wrapped_model_saves_under_unwrapped_names_and_carries_the_low_rank_artifacts(tmp_path):
     src = ToyDecoder(n_layers=2, hidden=256, kv=128, inter=384, seed=4)
     shared, bmap = make_artifacts(src, rank=16)

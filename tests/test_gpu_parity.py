@@ -234,6 +234,26 @@ def test_gemm_parity(M, oc, ic, rank, alpha, bias):
             assert np.abs(r_buf.float().cpu().numpy() - r_want).max() <= 4e-3
 
 
+@pytest.mark.parametrize("M,oc,ic,rank,alpha", [(64, 256, 2048, 1024, 1.0), (64, 256, 2048, 1024, 0.5),
+                                                (48, 384, 1024, 512, 1.0), (2560, 4096, 1024, 1024, 1.0)])
+def test_gemm_k_slices_that_start_inside_the_correction_steps(M, oc, ic, rank, alpha):
+    """Large rank against a short K: with the K steps of weights and correction cut into slices, some slices
+    begin (or lie wholly) in the correction steps.  Their first MMA must overwrite the accumulator, and an
+    accumulator a slice never touches must count as zero."""
+    rng = np.random.default_rng(M + rank)
+    lin = Linear(rng, oc, ic, rank=rank, bias=True)
+    x = rng.standard_normal((M, ic)).astype(np.float16)
+    R = (rng.standard_normal((rank, ic)) * 0.01).astype(np.float16)
+    out = new_out(M, lin, K.OUT_F32)
+    r_buf = torch.zeros(M, rank, dtype=torch.float16, device="cuda")
+    g = make_group(dev(x), [lin], [out], R_d=dev(R), r_buf=r_buf, r_mode=K.R_COMPUTE, alpha=alpha,
+                   kernel=K.KERNEL_GEMM, out_dtype=K.OUT_F32)
+    for _ in range(2):
+        out.fill_(float("nan"))
+        assert run_group(g) == 0 and status_ok(g) == 0
+        assert_close(out, lin.oracle(x, R, alpha=alpha), tag=f"gemm r{rank} ic{ic} M{M} alpha{alpha}")
+
+
 def test_gemm_group_and_cache_modes():
     """q computes r (one r product for the group), k and v load it; also the fused three-member call."""
     rng = np.random.default_rng(12)

@@ -38,6 +38,8 @@ def test_static_scratch_matches_workspace_entry_point_twice_in_a_row(oc, ic, M):
         # same kernel, same plan, same summation order: identical bits, and inside the oracle tolerances
         np.testing.assert_array_equal(got.cpu().numpy().view(np.uint16), want.cpu().numpy().view(np.uint16))
         assert_close(got, lin.oracle(x), tag=f"call {call}")
+    # callers of this entry point own no workspace: NULL addresses the built-in scratch's status word
+    assert ext().lib.glowq_w4a16_read_status(None, torch.cuda.current_stream().cuda_stream) == 0
 
 
 def test_static_scratch_rejects_what_does_not_fit():
