@@ -432,9 +432,10 @@ def run_gpu(args, shape):
 
     # the same step with every group call going through the C ABI's host-buffer entry point (copy in, launch, copy out,
     # synchronise - per group): what a caller without device-resident activations pays
-    host_entry = None
+    host_entry = dropin = None
     if world == 1 and not args.no_sweep:
         host_entry = host_entry_step(arm, stack, plan, min(args.steps, 20))
+        dropin = dropin_step(arm, stack, plan, min(args.steps, 50))
 
     # extra: prefill pass of the same stack through the tensor-core GEMM (reported, not the headline value)
     prefill = None
@@ -475,7 +476,7 @@ def run_gpu(args, shape):
                     "path": "pinned-host activations copied in and the last output copied out every step (torch "
                             "copy_ on the launching stream) around the graph-replayed step; see e2e_host_entry for the "
                             "C ABI's own host-buffer call"},
-            "e2e_host_entry": host_entry,
+            "e2e_host_entry": host_entry, "dropin": dropin,
             "gpu_launches": n_calls * args.steps,
             "roofline": {"bound": "hbm", "kernel": "gemv_stream_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "frac_of_8tbs": achieved / 8000.0,
@@ -544,6 +545,94 @@ def host_entry_step(arm, stack, plan, steps):
     return {"value": plan["M"] / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "h2d_bytes_per_step": bytes_in,
             "d2h_bytes_per_step": bytes_out, "calls_per_step": plan["n"],
             "path": "glowq_w4a16_group_forward_host per group (copy x in, launch, copy every output out, synchronise)"}
+
+
+def build_dropin_model(stack):
+    """The stack's linears behind the reference's own Python surface: a module tree with the artefact names
+    (model.layers.{i}.self_attn.q_proj ...) whose leaves are CudaW4A16Linear shells over copies of the stack's packed
+    tensors, patched by patch_svd_correction_wrappers from `shared` / `bmap` dicts in GlowQ's key scheme."""
+    import torch.nn as nn
+    import glowq_b200 as G
+    root = nn.Module()
+    root.model = nn.Module()
+    layers = nn.ModuleList()
+    shared, bmap = {}, {}
+    n_layers = len(stack.groups) // 4
+    for li in range(n_layers):
+        qkv, o, mlp, down = stack.groups[4 * li:4 * li + 4]
+        layer = nn.Module()
+        layer.self_attn, layer.mlp = nn.Module(), nn.Module()
+        for parent, grp, names, gk in ((layer.self_attn, qkv, ("q_proj", "k_proj", "v_proj"), f"layer{li}_qkv"),
+                                       (layer.mlp, mlp, ("gate_proj", "up_proj"), f"layer{li}_mlp")):
+            pname = "self_attn" if parent is layer.self_attn else "mlp"
+            for name, m in zip(names, grp.members):
+                setattr(parent, name, m.as_module())
+                if grp.enabled:
+                    shared[f"{gk}.B_shared"] = grp.R
+                    shared[f"{gk}.{name}.A"] = m.L
+                    bmap[f"model.layers.{li}.{pname}.{name}.weight"] = f"{gk}.B_shared"
+        for parent, grp, name, pname in ((layer.self_attn, o, "o_proj", "self_attn"), (layer.mlp, down, "down_proj", "mlp")):
+            setattr(parent, name, grp.members[0].as_module())
+            if grp.enabled:
+                mod = f"model.layers.{li}.{pname}.{name}"
+                shared[f"{mod}.A"], shared[f"{mod}.B"] = grp.members[0].L, grp.R
+                bmap[f"{mod}.weight"] = f"{mod}.B"
+        layers.append(layer)
+    root.model.layers = layers
+    G.patch_svd_correction_wrappers_cumulative(root, shared, bmap, {k.rsplit(".", 1)[0] if k.endswith(".B") else
+                                                                    k.replace(".B_shared", "") for k in bmap.values()}, 1.0)
+    return root
+
+
+def dropin_step(arm, stack, plan, steps):
+    """tokens/s of the same token step issued through the drop-in modules (convert -> patch -> module calls in the
+    order a decoder layer makes them: q, k, v, o, gate, up, down), eagerly from Python and replayed from a CUDA graph."""
+    torch = arm.torch
+    os.environ["W4A16_KERNEL_OUT_DTYPE"] = "fp16"       # what the reference's step3 sets before converting
+    model = build_dropin_model(stack)
+    x, xa, xi = plan["inputs"]["hidden"], plan["inputs"]["attn"], plan["inputs"]["inter"]
+    calls = []
+    for layer in model.model.layers:
+        a, m = layer.self_attn, layer.mlp
+        calls += [(a.q_proj, x), (a.k_proj, x), (a.v_proj, x), (a.o_proj, xa), (m.gate_proj, x), (m.up_proj, x),
+                  (m.down_proj, xi)]
+
+    def step():
+        out = None
+        for mod, inp in calls:
+            out = mod(inp)
+        return out
+
+    def time_it(run, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(arm.stream)
+        for _ in range(n):
+            run()
+        e1.record(arm.stream)
+        arm.stream.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    with torch.cuda.stream(arm.stream):
+        for _ in range(3):
+            step()
+        arm.stream.synchronize()
+        ms_eager = time_it(step, steps)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=arm.stream):
+            step()
+        for _ in range(3):
+            graph.replay()
+        arm.stream.synchronize()
+        ms_graph = time_it(graph.replay, steps)
+    M = plan["M"]
+    launches = sum(1 for mod, _ in calls if getattr(mod, "group_launcher", None) is None
+                   or mod.group_launcher.members[0] is mod)
+    del model, calls, graph
+    torch.cuda.empty_cache()
+    return {"value": M / (ms_graph * 1e-3), "unit": UNIT, "ms_per_step": ms_graph,
+            "eager_tokens_per_s": M / (ms_eager * 1e-3), "eager_ms_per_step": ms_eager, "launches_per_step": launches,
+            "path": "convert_to_cuda_w4a16-style modules + patch_svd_correction_wrappers, 7 module calls per layer in "
+                    "decoder order; `value` replays them from a CUDA graph, `eager_*` pays the Python dispatch"}
 
 
 def run_sweep(arm, args, main_stack=None):

@@ -159,11 +159,7 @@ struct GemvPlan {
 };
 
 size_t plan_smem(const GemvPlan& pl, int Mc, int stages) {
-  return 256 + static_cast<size_t>(stages) * kStageBytes +
-         static_cast<size_t>(kMetaDepth) * kTileRows * (pl.meta_gp * 2 + pl.meta_gw * 4) +
-         static_cast<size_t>(2 * kConsumerWarps) * kRowTiles * pl.NT * 512 + static_cast<size_t>(pl.NT) * 512 +
-         static_cast<size_t>(pl.gps) * pl.NT * 32 +
-         static_cast<size_t>(Mc) * pl.xs_stride;
+  return gemv_smem_layout_bytes(stages, pl.meta_gp, pl.meta_gw, pl.gps, pl.NT, Mc, pl.xs_stride);
 }
 
 GemvPlan make_plan(int M, int IC, int n_tiles, int rank, int sms, int split_k) {
@@ -203,7 +199,12 @@ GemvPlan make_plan(int M, int IC, int n_tiles, int rank, int sms, int split_k) {
           break;
         }
     }
-    if (pl.stages > 0 || pl.gps == kChunkGroups) break;  // fits, or K cannot be sliced any finer
+    if (pl.gps == kChunkGroups) break;  // K cannot be sliced any finer
+    // One or two tokens: two CTAs per SM (16 consumer warps) are worth more than long K slices, so keep slicing while
+    // only one CTA would fit (the per-group shared-memory footprint - staged x, converted scale pairs - grows with
+    // the slice length).  More tokens stage too much x for that; they take what fits.
+    const bool want_two = split_k <= 0 && Mc <= 2 && sk < 8 && n_tiles * (sk + 1) <= 8 * sms;
+    if (pl.stages > 0 && (pl.ctas_per_sm == 2 || !want_two)) break;
   }
   if (forced_stages > 0 && pl.stages > 0) pl.stages = std::max(2, std::min(forced_stages, pl.stages));
   pl.smem = plan_smem(pl, Mc, pl.stages);
@@ -323,7 +324,12 @@ int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cuda
     p.x_vec_ok = aligned16(x) && (g.x_stride % 8 == 0);
     p.xs_stride = pl.xs_stride;
     p.stages = pl.stages;
-    p.debug = g.reserved;
+#ifdef GLOWQ_GEMV_TRACE
+    static const int env_debug = env_int("GLOWQ_GEMV_DEBUG", 0);   // tuning builds only
+    p.debug = g.reserved | env_debug;
+#else
+    p.debug = 0;
+#endif
     p.meta_gp = pl.meta_gp;
     p.meta_gw = pl.meta_gw;
     int tb = 0;
@@ -354,8 +360,10 @@ int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cuda
     if (fast) {
       if (pl.stages < 2 || gemv_smem_bytes(p, pl.NT) > kSmemOnePerSm) return GLOWQ_ERR_UNSUPPORTED_SHAPE;
       // persistent grid: every CTA resident at once, a whole number of CTAs per K slice
-      // few R units: dedicated CTAs at the end of the grid; many (large rank x IC): every CTA runs its share first
-      p.n_r_ctas = p.n_r_units <= 32 ? p.n_r_units : 0;
+      // R units run on dedicated CTAs at the end of the grid (several units each when there are many), so that the
+      // r chain (R loads, MMAs, slot, release counter) overlaps the other CTAs' x staging and weight streaming
+      static const int max_r_ctas = env_int("GLOWQ_GEMV_R_CTAS", 96);
+      p.n_r_ctas = std::min(p.n_r_units, std::max(0, std::min(max_r_ctas, dev.sms * pl.ctas_per_sm / 3)));
       int grid = std::min(dev.sms * pl.ctas_per_sm - p.n_r_ctas, n_tiles * pl.SK);
       grid = std::max(pl.SK, grid / pl.SK * pl.SK) + p.n_r_ctas;
       p.l_cols = std::min(std::max(p.rank, 8), 256);
@@ -369,6 +377,34 @@ int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cuda
           rc = tensor_map_2d(&tm.l[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, d.L, p.rank, d.OC,
                              static_cast<uint64_t>(d.Lstride) * 2, p.l_cols, kTileRows);
         if (rc != GLOWQ_OK) return rc;
+      }
+      // L2 prefetch requests for the call that follows on this stream: its right factor, then a prefix of its packed
+      // rows in tile order (what its CTAs read first)
+      static const int pf_mb = env_int("GLOWQ_GEMV_PREFETCH_MB", 32);
+      static const int deep_pf = env_int("GLOWQ_GEMV_DEEP_PREFETCH", 1);
+      p.deep_prefetch = deep_pf;
+      p.n_pf = 0;
+      if (g.next != nullptr && pf_mb > 0 && m0 + kGemvMaxM >= g.M) {
+        const glowq_w4a16_group_t& nx = *g.next;
+        size_t budget = static_cast<size_t>(pf_mb) << 20;
+        auto add = [&](const void* ptr, size_t bytes) {
+          bytes = std::min(bytes, budget) & ~static_cast<size_t>(15);
+          if (ptr != nullptr && aligned16(ptr) && bytes >= 16 && p.n_pf < kMaxPrefetch) {
+            p.pf_ptr[p.n_pf] = static_cast<const unsigned char*>(ptr);
+            p.pf_bytes[p.n_pf] = static_cast<unsigned>(bytes);
+            ++p.n_pf;
+            budget -= bytes;
+          }
+        };
+        if (nx.IC > 0 && nx.n_members >= 1 && nx.n_members <= GLOWQ_MAX_MEMBERS) {
+          if (nx.r_mode == GLOWQ_R_COMPUTE && nx.R != nullptr && nx.rank > 0 && nx.R_stride >= nx.IC)
+            add(nx.R, (static_cast<size_t>(nx.rank - 1) * nx.R_stride + nx.IC) * 2);
+          for (int i = 0; i < nx.n_members; ++i) {
+            const auto& m = nx.members[i];
+            if (m.OC > 0 && m.weight_stride_i32 >= ceil_div(nx.IC, 8))
+              add(m.qweight, (static_cast<size_t>(m.OC - 1) * m.weight_stride_i32 + ceil_div(nx.IC, 8)) * 4);
+          }
+        }
       }
       e = launch_gemv_stream(p, tm, pl.NT, grid, stream);
       if (e != cudaSuccess) return fail_cuda(e);
@@ -466,7 +502,14 @@ int glowq_w4a16_group_forward(const glowq_w4a16_group_t* group) {
 int glowq_w4a16_group_forward_many(const glowq_w4a16_group_t* groups, int n) {
   if (!groups || n < 0) return GLOWQ_ERR_BAD_ARGUMENT;
   for (int i = 0; i < n; ++i) {
-    const int rc = glowq_w4a16_group_forward(groups + i);
+    int rc;
+    if (groups[i].next == nullptr && i + 1 < n) {   // the array successor is what follows on the stream
+      glowq_w4a16_group_t g = groups[i];
+      g.next = groups + i + 1;
+      rc = glowq_w4a16_group_forward(&g);
+    } else {
+      rc = glowq_w4a16_group_forward(groups + i);
+    }
     if (rc != GLOWQ_OK) return rc;
   }
   return GLOWQ_OK;

@@ -61,6 +61,14 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tmap, 
       "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
       : "memory");
 }
+// L2 prefetch requests (no shared memory involved): the box of a tensor map, or a flat byte range (16-byte aligned
+// address, size a multiple of 16).
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* tmap, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void l2_prefetch_bytes(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
 // 4-byte asynchronous copy global -> shared (LDGSTS) and its completion hook on an mbarrier: the arrive fires
 // once all of this thread's earlier cp.async copies have landed; it counts as one of the barrier's arrivals.
 __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
@@ -355,19 +363,23 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   constexpr int RT = kRowTiles;
   constexpr int NB = RT * NT;  // 16-row x 8-token fragment blocks per tile
 
-  // shared-memory carve-up (must match gemv_smem_bytes)
+  // shared-memory carve-up (must match gemv_smem_layout_bytes)
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);
   uint64_t* empty_bar = full_bar + kMaxStages;
-  uint64_t* meta_full = empty_bar + kMaxStages;
-  uint64_t* meta_empty = meta_full + kMetaDepth;
-  uint64_t* red_empty = meta_empty + kMetaDepth;     // [2]: the aux warp has drained a reduction buffer
+  uint64_t* meta_full = empty_bar + kMaxStages;       // [kMetaDepth]: a tile's raw scales / zero words have landed
+  uint64_t* cooked_full = meta_full + kMetaDepth;     // [kCookedDepth]: a tile's converted pairs are written
+  uint64_t* cooked_empty = cooked_full + kCookedDepth;  // ... and the consumer warps are done with them
+  uint64_t* red_empty = cooked_empty + kCookedDepth;  // [2]: the aux warp has drained a reduction buffer
   unsigned char* ring = smem + 256;
   const int meta_bytes = kTileRows * (p.meta_gp * 2 + p.meta_gw * 4);
   unsigned char* meta = ring + static_cast<size_t>(p.stages) * kStageBytes;
-  float* red = reinterpret_cast<float*>(meta + static_cast<size_t>(kMetaDepth) * meta_bytes);
+  const int cooked_bytes = p.gps * (kTileRows * 8);   // [group][row] float2 {scale * 2^24, -scale * zero}
+  unsigned char* cooked = meta + static_cast<size_t>(kMetaDepth) * meta_bytes;
+  float* red = reinterpret_cast<float*>(cooked + static_cast<size_t>(kCookedDepth) * cooked_bytes);
   float* fin = red + 2 * kConsumerWarps * NB * 128;  // red is double-buffered; fin serves the R units only
   float* xsum = fin + NT * 128;                      // [groups of the slice][8 NT]
   unsigned char* xs = reinterpret_cast<unsigned char*>(xsum + p.gps * (8 * NT));
+  unsigned char* zero_row = xs + static_cast<size_t>(p.M) * p.xs_stride;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int S = p.stages;
@@ -402,9 +414,10 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       mbar_init(full_bar + i, 1);
       mbar_init(empty_bar + i, kConsumerWarps);
     }
-    for (int i = 0; i < kMetaDepth; ++i) {
-      mbar_init(meta_full + i, 32);
-      mbar_init(meta_empty + i, kConsumerWarps);
+    for (int i = 0; i < kMetaDepth; ++i) mbar_init(meta_full + i, 32);
+    for (int i = 0; i < kCookedDepth; ++i) {
+      mbar_init(cooked_full + i, 1);
+      mbar_init(cooked_empty + i, kConsumerWarps);
     }
     mbar_init(red_empty + 0, 1);
     mbar_init(red_empty + 1, 1);
@@ -414,7 +427,8 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   if (threadIdx.x == 0) trace_event(p, 1);
   Ctx cx{&s_abort, p.ws_head + WS_STATUS, tuning_bits(p)};
   const uint32_t full_u32 = smem_u32(full_bar), empty_u32 = smem_u32(empty_bar);
-  const uint32_t mfull_u32 = smem_u32(meta_full), mempty_u32 = smem_u32(meta_empty);
+  const uint32_t mfull_u32 = smem_u32(meta_full);
+  const uint32_t cfull_u32 = smem_u32(cooked_full), cempty_u32 = smem_u32(cooked_empty);
   const uint32_t rempty_u32 = smem_u32(red_empty);
 
   if (warp == kConsumerWarps) {
@@ -425,6 +439,11 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     bool ok = true;
     for (int k = 0, tile; (tile = tile_at(k)) < p.n_tiles && ok; ++k) {
       const TileInfo ti = tile_info(p, tile, slice);
+      // one row tile ahead of the ring, the same chunk goes to L2: while the ring is full (launch prologue, epilogues)
+      // HBM keeps streaming, and the ring's own copies then hit L2
+      const int tile_next = tile_at(k + 1);
+      const bool have_next = p.deep_prefetch && tile_next < p.n_tiles;
+      const TileInfo ti_next = tile_info(p, have_next ? tile_next : tile, slice);
       for (int c = 0; c < n_chunks; ++c) {
         if (!(ok = mbar_wait_u32(empty_u32 + st * 8, ph ^ 1, cx))) break;
         if (lane == 0) {
@@ -434,6 +453,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
             mbar_arrive_expect_tx(full_bar + st, kStageBytes);
             tma_load_2d(ring + static_cast<size_t>(st) * kStageBytes, &tm.w[ti.mi], (g0 + c * kChunkGroups) * 16, ti.row0,
                         full_bar + st);
+            if (have_next) tma_prefetch_2d(&tm.w[ti_next.mi], (g0 + c * kChunkGroups) * 16, ti_next.row0);
           }
         }
         ++issued;
@@ -457,6 +477,18 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
         }
       }
     }
+    if (ok && p.n_pf > 0) {
+      // This CTA's own copies are all issued: ask L2 for its share of what the NEXT call on the stream reads first
+      // (slices of kPrefetchSlice bytes dealt round-robin over the grid's copy warps, one per lane and turn).
+      for (int r = 0; r < p.n_pf; ++r) {
+        const uint32_t bytes = p.pf_bytes[r];
+        const uint32_t n_slices = (bytes + kPrefetchSlice - 1) / kPrefetchSlice;
+        for (uint32_t sidx = blockIdx.x + lane * gridDim.x; sidx < n_slices; sidx += 32u * gridDim.x) {
+          const uint32_t off = sidx * kPrefetchSlice;
+          l2_prefetch_bytes(p.pf_ptr[r] + off, min(kPrefetchSlice, bytes - off));
+        }
+      }
+    }
     if (!ok && !(tuning_bits(p) & 2)) {
       // Draining: copies already issued still land in this CTA's shared memory; wait (bounded) for them so that
       // the CTA does not retire under an in-flight copy.
@@ -467,44 +499,79 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       }
     }
   } else if (warp == kConsumerWarps + 1) {
-    // ================================================================ aux warp: metadata prefetch + tile epilogues
-    // Lane r fetches row r's scales / zero words a few tiles ahead with asynchronous 4-byte copies (the warp
-    // never waits for its own loads).  Between prefetches it finishes tiles: once the eight consumer warps have
-    // parked their partial sums in a reduction buffer (named barrier 2 + buf) it adds them up, runs the split-K
-    // combine, bias and the store, and hands the buffer back.  Consumers therefore never wait for one another.
-    uint32_t slot = 0, ph = 0, buf = 0;
-    int issued = 0, done = 0;
-    int k_m = 0;
+    // ================================================================ aux warp: metadata + tile epilogues
+    // Lane r fetches row r's scales / zero words three tiles ahead with asynchronous 4-byte copies (the warp never
+    // waits for a load it has just issued), and one tile ahead of the consumers converts them ONCE per (row, group)
+    // into the fp32 pair {scale * 2^24, -scale * zero} the consumers' group epilogue multiplies with, laid out
+    // [group][row] (the consumer warps, four lanes per row, would otherwise each repeat the unpacking and the
+    // conversions - on the integer pipe, which is the busiest unit of this kernel).  Between that it finishes tiles:
+    // once the eight consumer warps have parked their partial sums in a reduction buffer (named barrier 2 + buf) it
+    // adds them up, runs the split-K combine, bias and the store, and hands the buffer back.  Consumers therefore
+    // never wait for one another; only a CTA's LAST tile is summed by the consumer warps themselves (when K is not
+    // sliced), because they have nothing else left to do and 256 threads finish it sooner than one warp.
+    uint32_t buf = 0;
+    int k_m = 0;   // next tile (k-th of this CTA) whose raw metadata gets prefetched; raw slot k % kMetaDepth
     bool ok = true;
-    for (int k = 0, tile; (tile = tile_at(k)) < p.n_tiles; ++k) {
-      while (ok && tile_at(k_m) < p.n_tiles && issued - done < kMetaDepth) {
-        const int tile_m = tile_at(k_m);
-        const TileInfo tm_i = tile_info(p, tile_m, slice);
-        const MemberDev& mbm = p.mem[tm_i.mi];
-        if (!(ok = mbar_wait_u32(mempty_u32 + slot * 8, ph ^ 1, cx))) break;
-        const int row = min(tm_i.row0 + lane, mbm.OC - 1);
-        unsigned char* mbase = meta + static_cast<size_t>(slot) * meta_bytes;
-        __half* ms = reinterpret_cast<__half*>(mbase) + lane * p.meta_gp;
-        uint32_t* mz = reinterpret_cast<uint32_t*>(mbase + kTileRows * p.meta_gp * 2) + lane * p.meta_gw;
-        const __half* srow = mbm.scales + static_cast<size_t>(row) * mbm.sstride + g0;
-        if (((mbm.sstride | g0) & 1) == 0 && ((reinterpret_cast<uintptr_t>(mbm.scales) & 3) == 0)) {
-          const int np_full = ng >> 1;
-          for (int pi = 0; pi < np_full; ++pi) cp_async4(ms + 2 * pi, srow + 2 * pi);
-          if (ng & 1) ms[ng - 1] = srow[ng - 1];  // odd tail: there may be no 4 readable bytes at the end of a row
-        } else {
-          for (int gl = 0; gl < ng; ++gl) ms[gl] = srow[gl];
-        }
-        const int32_t* zrow = mbm.qzeros + static_cast<size_t>(row) * mbm.zstride + (g0 >> 3);
-        const int nw = (ng + 7) >> 3;
-        for (int wi = 0; wi < nw; ++wi) cp_async4(mz + wi, zrow + wi);
-        cp_async_mbar_arrive(meta_full + slot);
-        if (++slot == kMetaDepth) {
-          slot = 0;
-          ph ^= 1;
-        }
-        ++issued;
-        ++k_m;
+    auto prefetch_raw = [&]() {
+      const int tile_m = tile_at(k_m);
+      const TileInfo tm_i = tile_info(p, tile_m, slice);
+      const MemberDev& mbm = p.mem[tm_i.mi];
+      const uint32_t slot = static_cast<uint32_t>(k_m % kMetaDepth);
+      const int row = min(tm_i.row0 + lane, mbm.OC - 1);
+      unsigned char* mbase = meta + static_cast<size_t>(slot) * meta_bytes;
+      __half* ms = reinterpret_cast<__half*>(mbase) + lane * p.meta_gp;
+      uint32_t* mz = reinterpret_cast<uint32_t*>(mbase + kTileRows * p.meta_gp * 2) + lane * p.meta_gw;
+      const __half* srow = mbm.scales + static_cast<size_t>(row) * mbm.sstride + g0;
+      if (((mbm.sstride | g0) & 1) == 0 && ((reinterpret_cast<uintptr_t>(mbm.scales) & 3) == 0)) {
+        const int np_full = ng >> 1;
+        for (int pi = 0; pi < np_full; ++pi) cp_async4(ms + 2 * pi, srow + 2 * pi);
+        if (ng & 1) ms[ng - 1] = srow[ng - 1];  // odd tail: there may be no 4 readable bytes at the end of a row
+      } else {
+        for (int gl = 0; gl < ng; ++gl) ms[gl] = srow[gl];
       }
+      const int32_t* zrow = mbm.qzeros + static_cast<size_t>(row) * mbm.zstride + (g0 >> 3);
+      const int nw = (ng + 7) >> 3;
+      for (int wi = 0; wi < nw; ++wi) cp_async4(mz + wi, zrow + wi);
+      cp_async_mbar_arrive(meta_full + slot);
+      ++k_m;
+    };
+    // convert the raw metadata of this CTA's kc-th tile (it was prefetched earlier) into cooked slot kc % kCookedDepth
+    auto cook = [&](int kc) {
+      const uint32_t rslot = static_cast<uint32_t>(kc % kMetaDepth), rph = static_cast<uint32_t>(kc / kMetaDepth) & 1u;
+      const uint32_t cslot = static_cast<uint32_t>(kc % kCookedDepth), cph = static_cast<uint32_t>(kc / kCookedDepth) & 1u;
+      ok = ok && mbar_wait_u32(mfull_u32 + rslot * 8, rph, cx);
+      ok = ok && mbar_wait_u32(cempty_u32 + cslot * 8, cph ^ 1, cx);
+      if (ok) {
+        const unsigned char* mbase = meta + static_cast<size_t>(rslot) * meta_bytes;
+        const __half* ms = reinterpret_cast<const __half*>(mbase) + lane * p.meta_gp;
+        const uint32_t* mz = reinterpret_cast<const uint32_t*>(mbase + kTileRows * p.meta_gp * 2) + lane * p.meta_gw;
+        float2* dst = reinterpret_cast<float2*>(cooked + static_cast<size_t>(cslot) * cooked_bytes) + lane;
+        for (int wi = 0; wi * 8 < ng; ++wi) {
+          const uint32_t zw = mz[wi];
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {
+            const int gl = wi * 8 + j;
+            if (gl < ng) {
+              const __half2 sp = *reinterpret_cast<const __half2*>(ms + gl);   // groups gl, gl + 1 (pitch is even)
+              const float2 sf = __half22float2(sp);
+              const float z0 = static_cast<float>((zw >> (4 * j)) & 0xFu), z1 = static_cast<float>((zw >> (4 * j + 4)) & 0xFu);
+              dst[gl * kTileRows] = make_float2(sf.x * 16777216.f, -sf.x * z0);
+              if (gl + 1 < ng) dst[(gl + 1) * kTileRows] = make_float2(sf.y * 16777216.f, -sf.y * z1);
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(cooked_full + cslot);
+    };
+    while (k_m < kMetaDepth && tile_at(k_m) < p.n_tiles) prefetch_raw();
+    if (tile_at(0) < p.n_tiles) cook(0);
+    for (int k = 0, tile; (tile = tile_at(k)) < p.n_tiles; ++k) {
+      // raw slot k % kMetaDepth was cooked in the previous round: refill it with the tile three ahead
+      if (k_m == k + kMetaDepth && tile_at(k_m) < p.n_tiles) prefetch_raw();
+      const bool last = tile_at(k + 1) >= p.n_tiles;
+      if (!last) cook(k + 1);
+      if (last && p.SK == 1) break;   // the consumer warps finish this tile themselves
 
       // ---- epilogue of `tile` (outputs may still be read by the previous kernel until it has completed)
       if (k == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -531,7 +598,6 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       __syncwarp();
       if (lane == 0) mbar_arrive(red_empty + buf);  // the consumers may refill this buffer
       buf ^= 1;
-      ++done;
       bool finalize = true;
       if (p.SK > 1) {
         // every K slice parks its tile; the last slice to arrive adds them up in slice order (deterministic)
@@ -606,30 +672,33 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     if (dep_wait_pending) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x == 0) trace_event(p, 2);
     if (!r_only || deal_all) stage_x(p, g0, ng, xs, xsum, 8 * NT);
-    consumer_sync();  // publishes xs / xsum
+    if (threadIdx.x < kZeroRowBytes / 4) reinterpret_cast<uint32_t*>(zero_row)[threadIdx.x] = 0u;
+    consumer_sync();  // publishes xs / xsum / the zero row
     if (threadIdx.x == 0) trace_event(p, 3);
 
-    // per-lane constant shared addresses: weight quad (warp's group, lane's 16 B, lane's row), x chunk, x sums
+    // per-lane constant shared addresses: weight quad (warp's group, lane's 16 B, lane's row), x chunk, x sums, the
+    // converted scale / zero pairs.  A token slot of the MMA that holds no token reads an all-zero row instead (its
+    // address does not advance), so that the loads below are unconditional.
     const uint32_t ring_lane = smem_u32(ring) + warp * 64 + t * 16 + g * kRowPitch;
-    const uint32_t x_lane = smem_u32(xs) + g * p.xs_stride + t * 16;
-    const uint32_t xsum_lane = smem_u32(xsum) + t * 8;
-    const uint32_t xtok8 = 8u * p.xs_stride;
-    const uint32_t meta_u32 = smem_u32(meta);
-    const uint32_t zshift = warp * 4;  // group gl = 8 c + warp: zero nibble `warp` of zero word c
+    const uint32_t xsum_lane = smem_u32(xsum) + warp * (32 * NT) + t * 8;
+    const uint32_t cooked_lane = smem_u32(cooked) + warp * (kTileRows * 8) + g * 8;
+    uint32_t x_lane[NT], x_step[NT];
     bool tokv[NT];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) tokv[nt] = (nt * 8 + g) < p.M;
+    for (int nt = 0; nt < NT; ++nt) {
+      tokv[nt] = (nt * 8 + g) < p.M;
+      x_lane[nt] = tokv[nt] ? smem_u32(xs) + (nt * 8 + g) * p.xs_stride + t * 16 + warp * 256 : smem_u32(zero_row) + t * 16;
+      x_step[nt] = tokv[nt] ? kChunkGroups * 256u : 0u;
+    }
 
-    uint32_t st = 0, ph = 0, slot = 0, mph = 0, rbuf = 0, rph = 0;
+    uint32_t st = 0, ph = 0, rbuf = 0, rph = 0;
     bool ok = true, r_ready = (p.r_mode != 1), rb_cached = false;
     uint4 rb_keep[NT];  // r fragments of this lane (first L stage): the same for every row tile of the CTA
     for (int k = 0, tile; (tile = tile_at(k)) < p.n_tiles; ++k) {
       const TileInfo ti = tile_info(p, tile, slice);
       const MemberDev& mb = p.mem[ti.mi];
-      ok = ok && mbar_wait_u32(mfull_u32 + slot * 8, mph, cx);
-      const uint32_t ms_lane = meta_u32 + slot * meta_bytes + (g * p.meta_gp + warp) * 2;
-      const uint32_t mz_lane = meta_u32 + slot * meta_bytes + kTileRows * p.meta_gp * 2 + g * p.meta_gw * 4;
-      const uint32_t ms_row8 = 8u * p.meta_gp * 2, mz_row8 = 8u * p.meta_gw * 4;
+      const uint32_t cslot = static_cast<uint32_t>(k % kCookedDepth), cph = static_cast<uint32_t>(k / kCookedDepth) & 1u;
+      ok = ok && mbar_wait_u32(cfull_u32 + cslot * 8, cph, cx);
 
       float acc[NB][4];
 #pragma unroll
@@ -640,11 +709,14 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       // activations were staged divided by 16, so every product carries the factor 2^-24, which goes into the
       // group's scale.  The zero-point leaves the inner loop too:
       //   sum_k (n_k - z) x_k = sum_k n_k x_k - z * sum_k x_k,   with sum_k x_k staged per (group, token).
+      uint32_t xa[NT];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) xa[nt] = x_lane[nt];
+      uint32_t ck = cooked_lane + cslot * cooked_bytes, xsu = xsum_lane;
       for (int c = 0; c < n_chunks; ++c) {
         ok = ok && mbar_wait_u32(full_u32 + st * 8, ph, cx);
         if (threadIdx.x == 0 && k == 0 && c == 0) trace_event(p, 4);
-        const int gl = c * kChunkGroups + warp;
-        if (ok && gl < ng && !(tuning_bits(p) & 1)) {
+        if (ok && c * kChunkGroups + warp < ng && !(tuning_bits(p) & 1)) {
           const uint32_t wbase = ring_lane + st * kStageBytes;
           uint4 W[RT][2];
 #pragma unroll
@@ -657,13 +729,12 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
           for (int j = 0; j < RT; ++j)
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) ag[j][nt][0] = ag[j][nt][1] = ag[j][nt][2] = ag[j][nt][3] = 0.f;
-          const uint32_t xg = x_lane + gl * 256;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             constexpr uint32_t MLO = 0x000F000Fu, MHI = 0x00F000F0u;
             uint4 xb[NT];
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) xb[nt] = tokv[nt] ? lds128(xg + nt * xtok8 + i * 64) : make_uint4(0, 0, 0, 0);
+            for (int nt = 0; nt < NT; ++nt) xb[nt] = lds128(xa[nt] + i * 64);
 #pragma unroll
             for (int j = 0; j < RT; ++j) {
               const uint32_t a = (i == 0) ? W[j][0].x : (i == 1) ? W[j][0].y : (i == 2) ? W[j][0].z : W[j][0].w;
@@ -676,24 +747,25 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
               }
             }
           }
+          // group epilogue: rows g, g+8 (row tile 0), g+16, g+24 (row tile 1) of this warp's group
 #pragma unroll
           for (int j = 0; j < RT; ++j) {
-            const float sA = lds_h2f(ms_lane + j * 2 * ms_row8 + c * 16);
-            const float sB = lds_h2f(ms_lane + j * 2 * ms_row8 + ms_row8 + c * 16);
-            const float zA = static_cast<float>((lds32(mz_lane + j * 2 * mz_row8 + c * 4) >> zshift) & 0xFu);
-            const float zB = static_cast<float>((lds32(mz_lane + j * 2 * mz_row8 + mz_row8 + c * 4) >> zshift) & 0xFu);
-            const float sA24 = sA * 16777216.f, sB24 = sB * 16777216.f, szA = -sA * zA, szB = -sB * zB;
+            const float2 pA = lds_f2(ck + (j * 16) * 8), pB = lds_f2(ck + (j * 16 + 8) * 8);  // {s * 2^24, -s * z}
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-              const float2 xs2 = lds_f2(xsum_lane + gl * (32 * NT) + nt * 32);
+              const float2 xs2 = lds_f2(xsu + nt * 32);
               float* a4 = acc[j * NT + nt];
-              a4[0] = fmaf(sA24, ag[j][nt][0], fmaf(szA, xs2.x, a4[0]));
-              a4[1] = fmaf(sA24, ag[j][nt][1], fmaf(szA, xs2.y, a4[1]));
-              a4[2] = fmaf(sB24, ag[j][nt][2], fmaf(szB, xs2.x, a4[2]));
-              a4[3] = fmaf(sB24, ag[j][nt][3], fmaf(szB, xs2.y, a4[3]));
+              a4[0] = fmaf(pA.x, ag[j][nt][0], fmaf(pA.y, xs2.x, a4[0]));
+              a4[1] = fmaf(pA.x, ag[j][nt][1], fmaf(pA.y, xs2.y, a4[1]));
+              a4[2] = fmaf(pB.x, ag[j][nt][2], fmaf(pB.y, xs2.x, a4[2]));
+              a4[3] = fmaf(pB.x, ag[j][nt][3], fmaf(pB.y, xs2.y, a4[3]));
             }
           }
         }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) xa[nt] += x_step[nt];
+        ck += kChunkGroups * (kTileRows * 8);
+        xsu += kChunkGroups * (32 * NT);
         __syncwarp();
         if (lane == 0) mbar_arrive_u32(empty_u32 + st * 8);
         if (++st == static_cast<uint32_t>(S)) {
@@ -761,13 +833,9 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
           for (int c = 0; c < 4; ++c) acc[b][c] = fmaf(mb.alpha, al[b][c], acc[b][c]);
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive_u32(mempty_u32 + slot * 8);
-      if (++slot == kMetaDepth) {
-        slot = 0;
-        mph ^= 1;
-      }
+      if (lane == 0) mbar_arrive_u32(cempty_u32 + cslot * 8);   // the aux warp may convert the tile after next into this slot
 
-      // park the partial sums for the aux warp and move on to the next tile
+      // park the partial sums
       ok = ok && mbar_wait_u32(rempty_u32 + rbuf * 8, rph ^ 1, cx);
       {
         float4* red4 = reinterpret_cast<float4*>(red) + static_cast<size_t>(rbuf) * kConsumerWarps * NB * 32;
@@ -775,6 +843,32 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
         for (int b = 0; b < NB; ++b)
           red4[(warp * NB + b) * 32 + lane] = make_float4(acc[b][0], acc[b][1], acc[b][2], acc[b][3]);
       }
+      if (p.SK == 1 && tile_at(k + 1) >= p.n_tiles) {
+        // This CTA's last tile (K not sliced): nothing is left to overlap with, so the 256 consumer threads add the
+        // eight partial sums themselves - one output element each per fragment block - instead of handing the
+        // tile to the single aux warp.
+        consumer_sync();
+        const float* redb = red + static_cast<size_t>(rbuf) * kConsumerWarps * NB * 128;
+        for (int e = threadIdx.x; e < NB * 128; e += kConsumerThreads) {
+          const int b = e >> 7, ln = (e & 127) >> 2, cc = e & 3;
+          const int j = b / NT, nt = b - j * NT;
+          const int row = ti.row0 + j * 16 + (ln >> 2) + ((cc & 2) ? 8 : 0);
+          const int tok = nt * 8 + (ln & 3) * 2 + (cc & 1);
+          if (row < mb.OC && tok < p.M) {
+            float o = 0.f;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) o += redb[((w * NB + b) * 32 + ln) * 4 + cc];
+            if (mb.bias) o += __half2float(mb.bias[row]);
+            const size_t idx = static_cast<size_t>(tok) * mb.out_stride + row;
+            if (p.out_fp32)
+              static_cast<float*>(mb.out)[idx] = o;
+            else
+              static_cast<__half*>(mb.out)[idx] = __float2half_rn(o);
+          }
+        }
+        break;
+      }
+      // ... and hand them to the aux warp, then move on to the next tile
       if (rbuf == 0)
         asm volatile("bar.arrive 2, %0;" ::"n"(kConsumerThreads + 32) : "memory");
       else
@@ -872,13 +966,7 @@ __global__ void __launch_bounds__(256) r_widen_kernel(const __half* r_buf, float
 
 // ---------------------------------------------------------------- host launchers (called from abi.cu)
 size_t gemv_smem_bytes(const GemvParams& p, int NT) {
-  size_t off = 256;
-  off += static_cast<size_t>(p.stages) * kStageBytes;
-  off += static_cast<size_t>(kMetaDepth) * kTileRows * (p.meta_gp * 2 + p.meta_gw * 4);
-  off += static_cast<size_t>(2 * kConsumerWarps) * kRowTiles * NT * 512 + static_cast<size_t>(NT) * 512;
-  off += static_cast<size_t>(p.gps) * NT * 32;
-  off += static_cast<size_t>(p.M) * p.xs_stride;
-  return off;
+  return gemv_smem_layout_bytes(p.stages, p.meta_gp, p.meta_gw, p.gps, NT, p.M, p.xs_stride);
 }
 
 template <int NT>

@@ -21,10 +21,30 @@ constexpr int kMetaDepth = 3;       // tiles of scale / zero-point metadata in f
 constexpr int kMaxStages = 8;
 constexpr unsigned kSpinLimit = 1u << 18;  // bound of every device-side wait loop
 
+constexpr int kCookedDepth = 2;     // tiles of converted (fp32) scale / zero-point pairs ahead of the consumers
+constexpr int kZeroRowBytes = 320;  // all-zero activation row for the token slots of an MMA that hold no token
+
+// Dynamic shared memory of one CTA of the weight-streaming kernel (the kernel's carve-up follows this order):
+// barriers | weight ring | raw metadata ring | converted metadata ring | reduction buffers | R-unit scratch |
+// x sums | staged x | zero row.
+inline size_t gemv_smem_layout_bytes(int stages, int meta_gp, int meta_gw, int gps, int NT, int M, int xs_stride) {
+  size_t off = 256;
+  off += static_cast<size_t>(stages) * kStageBytes;
+  off += static_cast<size_t>(kMetaDepth) * kTileRows * (meta_gp * 2 + meta_gw * 4);
+  off += static_cast<size_t>(kCookedDepth) * gps * (kTileRows * 8);
+  off += static_cast<size_t>(2 * kConsumerWarps) * kRowTiles * NT * 512 + static_cast<size_t>(NT) * 512;
+  off += static_cast<size_t>(gps) * NT * 32;
+  off += static_cast<size_t>(M) * xs_stride;
+  off += kZeroRowBytes;
+  return off;
+}
+
 // Workspace header (uint32 words); the rest of the workspace follows at kWsHeaderBytes.
 enum : int { WS_TICKET = 0, WS_R_DONE = 1, WS_EXIT = 2, WS_STATUS = 3, WS_HEADER_WORDS = 64 };
 constexpr size_t kWsHeaderBytes = WS_HEADER_WORDS * 4;
 constexpr int kMaxRTiles = 64;      // rank <= 1024
+constexpr int kMaxPrefetch = kMaxMembers + 1;
+constexpr unsigned kPrefetchSlice = 16u << 10;  // bytes per L2 prefetch request
 
 struct MemberDev {
   const int32_t* qweight;
@@ -64,6 +84,13 @@ struct GemvParams {
   int debug;                     // tuning experiments only (0 in production)
   int l_cols;                    // columns of L per pipeline stage: min(rank, 256)
   int meta_gp, meta_gw;          // per-row metadata pitch: scale halves, zero words (of one K slice)
+  int deep_prefetch;             // the copy warp also asks L2 for the same chunk of its NEXT row tile
+  // Byte ranges of the group call that follows on the stream (a prefix of its packed rows in tile order, its right
+  // factor): every CTA's copy warp asks L2 for its share once its own copies are issued, so that HBM keeps streaming
+  // through this launch's tail and the next launch's prologue.
+  int n_pf;
+  const unsigned char* pf_ptr[kMaxPrefetch];
+  unsigned pf_bytes[kMaxPrefetch];
   MemberDev mem[kMaxMembers];
 };
 

@@ -20,7 +20,7 @@ OUT_F16, OUT_F32 = 0, 1
 R_NONE, R_COMPUTE, R_LOAD = 0, 1, 2
 KERNEL_AUTO, KERNEL_GEMV, KERNEL_GEMM = 0, 1, 2
 MAX_MEMBERS = 4
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 
 class Member(ctypes.Structure):
@@ -38,6 +38,7 @@ class Group(ctypes.Structure):
                 ("R_stride", ctypes.c_int32), ("rank", ctypes.c_int32), ("group_size", ctypes.c_int32),
                 ("r_mode", ctypes.c_int32), ("out_dtype", ctypes.c_int32), ("kernel", ctypes.c_int32),
                 ("n_members", ctypes.c_int32), ("split_k", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("next", ctypes.c_void_p),     # address of the Group that follows on the stream, or None
                 ("members", Member * MAX_MEMBERS)]
 
 

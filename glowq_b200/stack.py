@@ -201,9 +201,9 @@ class LinearStack:
 
     # ------------------------------------------------------------------ launch plans
     def plan(self, M: int, *, corrected: bool = True, fuse_groups: bool = True, kernel: int = K.KERNEL_AUTO,
-             out_dtype: int = K.OUT_F16, split_k: int = 0):
+             out_dtype: int = K.OUT_F16, split_k: int = 0, chain: bool = True):
         """Build (once per configuration) the ctypes array of group calls for one token step of M tokens."""
-        key = (M, corrected, fuse_groups, kernel, out_dtype, split_k)
+        key = (M, corrected, fuse_groups, kernel, out_dtype, split_k, chain)
         if key in self._plans:
             return self._plans[key]
         s = self.shape
@@ -258,6 +258,9 @@ class LinearStack:
             keep += [outs, r_buf]
             group_outs.append(outs)
         arr = (K.Group * len(calls))(*calls)
+        if chain:   # tell every call what follows it on the stream (the last one: the next step's first call)
+            for i in range(len(calls)):
+                arr[i].next = ctypes.addressof(arr[(i + 1) % len(calls)])
         plan = {"calls": arr, "n": len(calls), "inputs": inputs, "full_inputs": full, "keep": keep,
                 "last_out": keep[-2][-1], "M": M, "group_outs": group_outs}
         self._plans[key] = plan

@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define GLOWQ_W4A16_ABI_VERSION 1
+#define GLOWQ_W4A16_ABI_VERSION 2
 
 enum {
   GLOWQ_OK = 0,
@@ -98,6 +98,12 @@ typedef struct glowq_w4a16_group {
   int32_t n_members;
   int32_t split_k;        /* 0 = choose; >0 forces the number of K slices of the GEMV         */
   int32_t reserved;       /* must be 0 (GLOWQ_ERR_BAD_ARGUMENT otherwise)                       */
+  /* Optional hint: the group call that will follow this one on the same stream (NULL = unknown).  Only its
+   * pointers and sizes are read, at call time: the streaming kernel asks L2 for the head of that call's packed
+   * weights and its right factor while its own launch drains, so that HBM does not idle between launches.
+   * Nothing is computed for `next`, and a wrong hint costs bandwidth, not correctness.  The reference has
+   * no counterpart (its launches are independent: csrc/gemv_w4a16.cu:194-211). */
+  const struct glowq_w4a16_group* next;
   glowq_w4a16_member_t members[GLOWQ_MAX_MEMBERS];
 } glowq_w4a16_group_t;
 
@@ -139,7 +145,7 @@ int glowq_w4a16_group_forward(const glowq_w4a16_group_t* group);
 
 /* `n` group calls issued back to back on their streams, in array order (one C call for a whole token step:
  * the reference pays one Python dispatch per module, src/cuda_w4a16/linear.py:155-187).  Stops at and
- * returns the first failing status. */
+ * returns the first failing status.  A call whose `next` is NULL is given its array successor as the hint. */
 int glowq_w4a16_group_forward_many(const glowq_w4a16_group_t* groups, int n);
 
 /* Same call with HOST activations: copies x_host[M, IC] (fp16, dense) to group->x, runs the group,

@@ -9,6 +9,7 @@ r = R x), load (r is read from the group's buffer)."""
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import sys
@@ -47,6 +48,7 @@ def main():
     ap.add_argument("--modes", default="plain,corr")
     ap.add_argument("--split-k", type=int, default=0)
     ap.add_argument("--iters", type=int, default=200)
+    ap.add_argument("--no-chain", action="store_true", help="leave the `next` hint of every call empty")
     ap.add_argument("--kernel", type=int, default=0, help="0 auto, 1 weight-streaming kernel, 2 tensor-core GEMM")
     args = ap.parse_args()
     ext = K.load_w4a16_extension()
@@ -94,6 +96,9 @@ def main():
                     keep += [outs, ws, r_buf]
                 arr = (K.Group * len(groups))(*groups)
                 n = len(groups)
+                if not args.no_chain:   # every launch names the one that follows it on the stream
+                    for i in range(n):
+                        arr[i].next = ctypes.addressof(arr[(i + 1) % n])
                 with torch.cuda.stream(st):
                     for _ in range(2):
                         ext.check(ext.lib.glowq_w4a16_group_forward_many(arr, n))

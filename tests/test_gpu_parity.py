@@ -416,15 +416,29 @@ def test_host_buffer_entry_point():
 
 
 # ---------------------------------------------------------------------------------------------- Python surface
-def test_toy_model_through_wrappers_matches_reference(golden_toy, monkeypatch):
-    """convert -> patch -> call in HF order on the GPU; outputs vs what the reference modules produced on CPU."""
+@pytest.mark.parametrize("fuse", ["1", "0"])
+def test_toy_model_through_wrappers_matches_reference(golden_toy, monkeypatch, fuse):
+    """convert -> patch -> call in HF order on the GPU; outputs vs what the reference modules produced on CPU.
+    fuse = 1: the patcher's group launchers issue one library call per q/k/v and gate/up group (k, v and up are
+    served from the producer's launch); fuse = 0: one call per module (the wrapper protocol)."""
     monkeypatch.setenv("W4A16_KERNEL_OUT_DTYPE", "fp16")
+    monkeypatch.setenv("GLOWQ_FUSE_GROUPS", fuse)
     from toy_model import ToyDecoder, make_artifacts
     import glowq_b200 as G
+    from glowq_b200.cuda_w4a16.linear import CudaW4A16Linear
     model = G.convert_to_cuda_w4a16(ToyDecoder(), 128)
     shared, bmap = make_artifacts(model)
     model = model.cuda()
     G.patch_svd_correction_wrappers(model, shared, bmap, 1.0)
+    launches = []
+    real_launch = CudaW4A16Linear.launch
+    monkeypatch.setattr(CudaW4A16Linear, "launch", lambda self, *a, **k: (launches.append(1), real_launch(self, *a, **k))[1])
+    q0 = model.proj(0, "self_attn.q_proj")
+    assert (q0.group_launcher is not None) == (fuse == "1")
+    if fuse == "1":
+        assert [w.role for w in q0.group_launcher.members] == ["q", "k", "v"]
+        assert model.proj(0, "self_attn.k_proj").group_launcher is q0.group_launcher
+        assert q0.group_launcher.next_launcher is model.proj(0, "self_attn.o_proj").group_launcher
     for M in (1, 5):
         x, xi = dev(golden_toy[f"x{M}"]), dev(golden_toy[f"xi{M}"])
         for li in range(2):
@@ -432,12 +446,28 @@ def test_toy_model_through_wrappers_matches_reference(golden_toy, monkeypatch):
                 y = model.proj(li, p)(xi if p.endswith("down_proj") else x)
                 assert y.dtype == torch.float16
                 assert_close(y, golden_toy[f"y{M}.{li}.{p}"].astype(np.float32), tag=f"{li}.{p}")
+    # fused: every call went through a group launcher; per module: 7 launches per layer and token count
+    assert len(launches) == (0 if fuse == "1" else 2 * 2 * 7)
+    # a consumer that is called with ANOTHER tensor than its producer saw computes for itself
+    x = dev(golden_toy["x5"])
+    model.proj(0, "self_attn.q_proj")(x)
+    other = (x * 0.5).contiguous()
+    y = model.proj(0, "self_attn.k_proj")(other)
+    assert_close(y * 2, golden_toy["y5.0.self_attn.k_proj"].astype(np.float32), tol_abs=4e-2, tol_rel=2e-3, tag="miss")
     # 3-D input keeps its leading dims; alpha 0 equals the bare module
     w = model.proj(0, "self_attn.q_proj")
     x3 = torch.randn(2, 3, 256, device="cuda", dtype=torch.float16)
     assert tuple(w(x3).shape) == (2, 3, 256)
-    w.alpha_svd = 0.0
+    for name in ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"):
+        model.proj(0, name).alpha_svd = 0.0
     torch.testing.assert_close(w(x3), w.inner(x3))
+    k = model.proj(0, "self_attn.k_proj")
+    torch.testing.assert_close(k(x3), k.inner(x3))       # nothing kept from an earlier call is served
+    # alpha 0 on one member only: it gets the bare product, the others keep their correction
+    model.proj(0, "self_attn.q_proj").alpha_svd = 1.0
+    y_q = w(x3)
+    torch.testing.assert_close(k(x3), k.inner(x3), rtol=2e-3, atol=2e-3)
+    assert float((y_q - w.inner(x3)).abs().max()) > 0
 
 
 @pytest.mark.gpu

@@ -33,26 +33,34 @@ def _worker(rank, world, port, q):
             got = ar.all_reduce(x.clone())
             torch.cuda.synchronize()
             worst = max(worst, float((got.float() - want).abs().max()))
-        # replay from a CUDA graph: the collective is an ordinary kernel
-        x = torch.randn(3072, generator=gen, device=dev).half()
-        keep = x.clone()
-        want = x.float().clone()
-        dist.all_reduce(want)
+        # replay from a CUDA graph: the collective is an ordinary kernel.  The graph holds two calls on alternating
+        # sites (a site may only be reused once every rank has finished its previous call on it, which the call on the
+        # other site in between guarantees), and the data change between replays.
+        xa = torch.zeros(3072, dtype=torch.float16, device=dev)
+        xb = torch.zeros(4 * 3072, dtype=torch.float16, device=dev)
         s = torch.cuda.Stream(dev)
         with torch.cuda.stream(s):
-            ar.all_reduce(x, site=0)
-            ar.all_reduce(x, site=1)
+            ar.all_reduce(xa, site=0)
+            ar.all_reduce(xb, site=1)
             s.synchronize()
             g = torch.cuda.CUDAGraph()
-            x.copy_(keep)
             with torch.cuda.graph(g, stream=s):
-                ar.all_reduce(x, site=0)
+                ar.all_reduce(xa, site=0)
+                ar.all_reduce(xb, site=1)
             s.synchronize()
-            for _ in range(3):
-                x.copy_(keep)
+            for rep in range(4):
+                va = torch.randn(3072, generator=gen, device=dev).half()
+                vb = torch.randn(4 * 3072, generator=gen, device=dev).half()
+                wa, wb = va.float().clone(), vb.float().clone()
+                s.synchronize()
+                dist.all_reduce(wa)
+                dist.all_reduce(wb)
+                torch.cuda.synchronize()
+                xa.copy_(va)
+                xb.copy_(vb)
                 g.replay()
-            s.synchronize()
-        worst = max(worst, float((x.float() - want).abs().max()))
+                s.synchronize()
+                worst = max(worst, float((xa.float() - wa).abs().max()), float((xb.float() - wb).abs().max()))
         q.put((rank, worst, ar.status()))
     finally:
         dist.destroy_process_group()
