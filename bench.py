@@ -45,6 +45,9 @@ def parse_args():
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="with N > 1: the library's peer-store all-reduce inside one CUDA graph per step (default), or "
                          "NCCL all-reduces between per-segment graphs")
+    ap.add_argument("--no-push", action="store_true",
+                    help="with N > 1: keep the peer all-reduce a launch of its own instead of letting the row-split "
+                         "linears store their partial sums to the peers from their own epilogue")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the extra `sweep` and `e2e_host_entry` measurements")
@@ -280,10 +283,15 @@ class GpuArm:
                 start = idx
         lib, check = stack.ext.lib, stack.ext.check
         if self.peer_ar is not None and all(t.numel() <= PEER_AR_MAX_ELEMS for _, _, t in segs):
+            pushed = all(arr[n - 1].push for arr, n, _ in segs)    # the row-split launches store to the peers themselves
+
             def step():
                 for i, (arr, n, t) in enumerate(segs):
                     check(lib.glowq_w4a16_group_forward_many(arr, n), "group_forward_many")
-                    self.peer_ar.all_reduce(t, site=i & 1)
+                    if pushed:
+                        self.peer_ar.finish(t, site=i & 1)
+                    else:
+                        self.peer_ar.all_reduce(t, site=i & 1)
             return step, None
 
         def step():
@@ -345,7 +353,8 @@ class GpuArm:
         """Time one decode configuration; returns (ms per step, run callable, plan)."""
         torch = self.torch
         with torch.cuda.stream(self.stream):
-            plan = stack.plan(M, corrected=corrected, fuse_groups=not self.args.unfused, split_k=self.args.split_k)
+            plan = stack.plan(M, corrected=corrected, fuse_groups=not self.args.unfused, split_k=self.args.split_k,
+                              push=self.peer_ar if (self.world > 1 and not self.args.no_push) else None)
         ms, run = self.timed(stack, self.make_step(stack, plan), steps, warmup, not self.args.no_graph)
         stack.check_status(plan)
         return ms, run, plan
@@ -467,7 +476,8 @@ def run_gpu(args, shape):
             "vs_baseline": None, "dtype": "f32 accumulate over fp16 x int4 (tensor-core MMA), fp16 out",
             "data": "synthetic", "config": workload_config(args, shape),
             "plan": {"parallelism": f"tp{world}", "cuda_graph": use_graph,
-                     "collective": (("peer-store all-reduce kernel" if arm.peer_ar is not None else "nccl")
+                     "collective": ((("peer stores from the row-split launch + finishing kernel" if not args.no_push and M <= 8
+                                      else "peer-store all-reduce kernel") if arm.peer_ar is not None else "nccl")
                                     if world > 1 else None),
                      "launches_per_layer": calls_per_layer},
             "clocks": {k: clocks.get(k) for k in ("sm_mhz", "sm_max_mhz", "reasons")},

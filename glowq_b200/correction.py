@@ -323,6 +323,10 @@ def _patch(model, shared, bmap, alpha_svd, groups_to_patch: Optional[Set[str]], 
     if verbose:
         print(f"SVD Correction Patching Summary: {patched} patched, {skipped} skipped")
     if _fuse_enabled():
+        # launch order = module order of the model (q, k, v, o, gate, up, down within a layer), whatever the order of
+        # the map's entries
+        pos = {id(m): i for i, (_, m) in enumerate(model.named_modules())}
+        wrapped.sort(key=lambda gw: pos.get(id(gw[1]), len(pos)))
         _install_launchers(wrapped)
     return model
 

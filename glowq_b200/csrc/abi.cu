@@ -245,7 +245,7 @@ int validate_group(const glowq_w4a16_group_t& g) {
   if (g.out_dtype != GLOWQ_OUT_F16 && g.out_dtype != GLOWQ_OUT_F32) return GLOWQ_ERR_BAD_ARGUMENT;
 #if !defined(GLOWQ_GEMV_TRACE) && !defined(GLOWQ_GEMM_TRACE)
   // reserved fields must be zero: a struct that was not cleared is refused instead of steering anything
-  if (g.reserved != 0) return GLOWQ_ERR_BAD_ARGUMENT;
+  if (g.reserved != 0 || g.reserved2 != 0 || g.reserved3 != 0) return GLOWQ_ERR_BAD_ARGUMENT;
   for (int i = 0; i < g.n_members; ++i)
     if (g.members[i].reserved != 0) return GLOWQ_ERR_BAD_ARGUMENT;
 #endif
@@ -261,6 +261,25 @@ int validate_group(const glowq_w4a16_group_t& g) {
     if (g.r_mode != GLOWQ_R_NONE && g.members[i].L && g.members[i].L_stride < g.rank) return GLOWQ_ERR_BAD_STRIDE;
   }
   if (!g.workspace) return GLOWQ_ERR_BAD_ARGUMENT;
+  if (g.norm_weight != nullptr) {
+    if (g.M > kGemvMaxM || g.kernel == GLOWQ_KERNEL_GEMM || (g.IC & 7) || (g.x_stride & 7) || !aligned16(g.x) ||
+        !aligned16(g.norm_weight) || !aligned16(g.residual) || !aligned16(g.hidden_out) || !(g.norm_eps >= 0.f))
+      return GLOWQ_ERR_UNSUPPORTED_SHAPE;
+  } else if (g.residual != nullptr || g.hidden_out != nullptr) {
+    return GLOWQ_ERR_BAD_ARGUMENT;   // these belong to the fused norm
+  }
+  if (g.push != nullptr) {
+    const glowq_w4a16_peers_t& pp = *g.push;
+    if (pp.world < 1 || pp.world > GLOWQ_MAX_RANKS || pp.rank < 0 || pp.rank >= pp.world || !pp.epoch)
+      return GLOWQ_ERR_BAD_ARGUMENT;
+    for (int r = 0; r < pp.world; ++r)
+      if (!pp.buf[r] || !pp.flag[r]) return GLOWQ_ERR_BAD_ARGUMENT;
+    const long long n = static_cast<long long>(g.M) * g.members[0].OC;
+    if (g.n_members != 1 || g.out_dtype != GLOWQ_OUT_F16 || g.members[0].out_stride != g.members[0].OC ||
+        g.M > kGemvMaxM || n > pp.max_n || (n & 7) || g.push_site < 0 || g.push_site >= pp.sites ||
+        g.kernel == GLOWQ_KERNEL_GEMM)
+      return GLOWQ_ERR_UNSUPPORTED_SHAPE;
+  }
   return GLOWQ_OK;
 }
 
@@ -356,6 +375,24 @@ int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cuda
     }
     if (p.r_mode != GLOWQ_R_NONE && !any_corr && p.r_mode == GLOWQ_R_LOAD) p.r_mode = GLOWQ_R_NONE;
 
+    p.norm_w = static_cast<const __half*>(g.norm_weight);
+    p.residual = static_cast<const __half*>(g.residual);
+    p.hidden_out = static_cast<__half*>(g.hidden_out);
+    p.norm_eps = g.norm_eps;
+    if (p.norm_w != nullptr && !fast) return GLOWQ_ERR_UNSUPPORTED_SHAPE;
+    p.push_world = 0;
+    if (g.push != nullptr) {
+      if (!fast) return GLOWQ_ERR_UNSUPPORTED_SHAPE;   // the any-layout kernels do not push
+      const glowq_w4a16_peers_t& pp = *g.push;
+      p.push_world = pp.world;
+      const size_t slot = (static_cast<size_t>(g.push_site) * pp.world + pp.rank) * pp.max_n;
+      for (int r = 0; r < pp.world; ++r) {
+        p.push_slot[r] = static_cast<__half*>(pp.buf[r]) + slot;
+        p.push_flag[r] = static_cast<uint32_t*>(pp.flag[r]) + g.push_site * pp.world + pp.rank;
+      }
+      p.push_epoch = static_cast<uint32_t*>(pp.epoch) + g.push_site;
+    }
+
     cudaError_t e;
     if (fast) {
       if (pl.stages < 2 || gemv_smem_bytes(p, pl.NT) > kSmemOnePerSm) return GLOWQ_ERR_UNSUPPORTED_SHAPE;
@@ -363,7 +400,18 @@ int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cuda
       // R units run on dedicated CTAs at the end of the grid (several units each when there are many), so that the
       // r chain (R loads, MMAs, slot, release counter) overlaps the other CTAs' x staging and weight streaming
       static const int max_r_ctas = env_int("GLOWQ_GEMV_R_CTAS", 96);
-      p.n_r_ctas = std::min(p.n_r_units, std::max(0, std::min(max_r_ctas, dev.sms * pl.ctas_per_sm / 3)));
+      {
+        const int cap = dev.sms * pl.ctas_per_sm;
+        int want = std::min(p.n_r_units, max_r_ctas);
+        if (pl.SK > 1) {
+          // K slices: the R CTAs take no row tiles afterwards, so give them the CTA slots that do not add a round
+          // of tiles to the slices (at least a few, or r would arrive long after the first tiles are done)
+          const int rounds = ceil_div(n_tiles * pl.SK, cap);
+          const int spare = cap - pl.SK * ceil_div(n_tiles, rounds);
+          want = std::min(p.n_r_units, std::max(std::min(spare, max_r_ctas), std::min(max_r_ctas, 16)));
+        }
+        p.n_r_ctas = std::max(0, std::min(want, cap / 3));
+      }
       int grid = std::min(dev.sms * pl.ctas_per_sm - p.n_r_ctas, n_tiles * pl.SK);
       grid = std::max(pl.SK, grid / pl.SK * pl.SK) + p.n_r_ctas;
       p.l_cols = std::min(std::max(p.rank, 8), 256);

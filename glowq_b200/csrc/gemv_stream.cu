@@ -112,11 +112,72 @@ __device__ __forceinline__ void trace_event(const GemvParams& p, int e) {
 }
 
 // ---------------------------------------------------------------- activations
+// Fused residual add + RMSNorm (HF LlamaRMSNorm / Qwen2RMSNorm semantics): h = fp16(x + residual),
+// xn = w * fp16(h * rstd) with rstd = rsqrt(mean(h^2) + eps) in fp32.  Eight consecutive columns k .. k+7 of token m.
+__device__ __forceinline__ uint4 residual_add8(const GemvParams& p, uint4 xv, int m, int k) {
+  if (p.residual == nullptr) return xv;
+  const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + static_cast<size_t>(m) * p.x_stride + k);
+  const __half2* x2 = reinterpret_cast<const __half2*>(&xv);
+  const __half2* r2 = reinterpret_cast<const __half2*>(&rv);
+  uint4 out;
+  __half2* o2 = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) o2[e] = __hadd2(x2[e], r2[e]);
+  return out;
+}
+__device__ __forceinline__ uint4 norm_x8(const GemvParams& p, uint4 xv, int m, int k, float rstd) {
+  const uint4 hv = residual_add8(p, xv, m, k);
+  const uint4 wv = *reinterpret_cast<const uint4*>(p.norm_w + k);
+  const __half2* h2 = reinterpret_cast<const __half2*>(&hv);
+  const __half2* w2 = reinterpret_cast<const __half2*>(&wv);
+  uint4 out;
+  __half2* o2 = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = __half22float2(h2[e]);
+    o2[e] = __hmul2(w2[e], __floats2half2_rn(f.x * rstd, f.y * rstd));
+  }
+  return out;
+}
+// rstd of every token row into s_rstd[0..M) (all consumer threads take part; `part` is scratch of 64 floats), and, on
+// CTA 0, h -> hidden_out.  IC is a multiple of 8 and the rows are 16-byte aligned (checked on the host).
+__device__ __forceinline__ void norm_stats(const GemvParams& p, float* part, float* s_rstd) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nv = p.IC >> 3;
+  for (int m = 0; m < p.M; ++m) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < nv; c += kConsumerThreads) {
+      const uint4 xv = *reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(m) * p.x_stride + 8 * c);
+      const uint4 hv = residual_add8(p, xv, m, 8 * c);
+      if (p.hidden_out != nullptr && blockIdx.x == 0)
+        *reinterpret_cast<uint4*>(p.hidden_out + static_cast<size_t>(m) * p.x_stride + 8 * c) = hv;
+      const __half2* h2 = reinterpret_cast<const __half2*>(&hv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(h2[e]);
+        ss = fmaf(f.x, f.x, fmaf(f.y, f.y, ss));
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) part[warp * 8 + m] = ss;
+  }
+  consumer_sync();
+  if (threadIdx.x < p.M) {
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) tot += part[w * 8 + threadIdx.x];
+    s_rstd[threadIdx.x] = rsqrtf(tot / static_cast<float>(p.IC) + p.norm_eps);
+  }
+  consumer_sync();
+}
+
 // Stage x[0:M, g0*128 : (g0+ng)*128) into shared memory in MMA B-fragment order: for token m and group gl,
 // 16-byte chunk (i*4 + t) holds the columns 32t+8i+{0,4,1,5,2,6,3,7} of that group, the ones at odd positions of
 // a packed word (1,5,3,7) multiplied by 1/16 (see the consumer loop), and xsum[gl][m] = sum of the group's x in
 // fp32 (for the zero-point term).  Consumer threads only.
-__device__ __forceinline__ void stage_x(const GemvParams& p, int g0, int ng, unsigned char* xs, float* xsum, int mpad) {
+__device__ __forceinline__ void stage_x(const GemvParams& p, int g0, int ng, unsigned char* xs, float* xsum, int mpad,
+                                        const float* s_rstd) {
   constexpr int kBatch = 4;  // global loads in flight per thread before any of them is consumed
   const int per_tok = ng * 16;
   const int total = p.M * per_tok;
@@ -137,6 +198,7 @@ __device__ __forceinline__ void stage_x(const GemvParams& p, int g0, int ng, uns
         const __half* src = p.x + static_cast<size_t>(m) * p.x_stride + k;
         if (p.x_vec_ok && k + 8 <= p.IC) {
           v[b] = *reinterpret_cast<const uint4*>(src);
+          if (p.norm_w != nullptr) v[b] = norm_x8(p, v[b], m, k, s_rstd[m]);
         } else {
           __align__(16) __half tmp[8];
 #pragma unroll
@@ -175,15 +237,19 @@ __device__ __forceinline__ uint4 lds128(uint32_t a) {
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
   return v;
 }
-__device__ __forceinline__ uint32_t lds32(uint32_t a) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+// The same loads with a compile-time byte offset folded into the instruction (an address register plus an immediate
+// costs no integer add; a sum computed in C++ and passed to the asm statement does).
+template <int OFF>
+__device__ __forceinline__ uint4 lds128_at(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a), "n"(OFF));
   return v;
 }
-__device__ __forceinline__ float lds_h2f(uint32_t a) {
-  unsigned short v;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
-  return __half2float(__ushort_as_half(v));
+template <int OFF>
+__device__ __forceinline__ float2 lds_f2_at(uint32_t a) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2+%3];" : "=f"(v.x), "=f"(v.y) : "r"(a), "n"(OFF));
+  return v;
 }
 __device__ __forceinline__ float2 lds_f2(uint32_t a) {
   float2 v;
@@ -241,67 +307,109 @@ __device__ __forceinline__ void cross_warp_reduce(float (&acc)[NB][4], float* re
   consumer_sync();
 }
 
-// One R unit: rows [16 rt, 16 rt + 16) of R times the columns of K slice ks (gpr groups), tokens 0..M-1.  The
-// fp32 result goes to the unit's own slot of r_partial and the release counter is bumped; whoever needs r adds
-// the SKr slots of an R tile in slot order (so every reader, and r_buf, see the same bits).
+// R units u0, u0 + ustride, ... of this CTA.  One unit: rows [16 rt, 16 rt + 16) of R times the columns of K slice
+// ks (gpr groups; warp w takes groups w, w + 8, ...), tokens 0..M-1.  The fp32 result goes to the unit's own slot of
+// r_partial; whoever needs r adds the SKr slots of an R tile in slot order (so every reader, and r_buf, see the same
+// bits).  R is static: the first round's loads and L2 prefetch requests for every later round of the CTA go out
+// before the wait for the previous kernel, and the CTA publishes all of its units with ONE fence and one add to the
+// release counter - readers need every unit anyway.
 template <int NT>
-__device__ __forceinline__ void r_unit(const GemvParams& p, int unit, float* red, float* fin, bool& dep_wait_pending) {
+__device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride, float* red, float* fin,
+                                        bool& dep_wait_pending, const float* s_rstd) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int rt = unit / p.SKr, ks = unit - rt * p.SKr;
-  const int j0 = rt * kRTileRows;
-  const int gbase = ks * p.gpr, ng = min(p.gpr, p.G - gbase);
-  const __half* rowA = p.R + static_cast<size_t>(min(j0 + g, p.rank - 1)) * p.R_stride;
-  const __half* rowB = p.R + static_cast<size_t>(min(j0 + g + 8, p.rank - 1)) * p.R_stride;
-  float acc[NT][4];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-  for (int gl = warp; gl < ng; gl += kConsumerWarps) {
-    const int kb = (gbase + gl) * kGroup + 32 * t;
-    uint4 a[4], b[4];
+  if (u0 >= p.n_r_units) return;
+  uint4 a[4], b[4];
+  // one round of a unit for this warp: 16 rows x 128 columns (group gl of the unit's K slice); `fetch` false only asks
+  // L2 for the lines (no registers are held, the loads that follow later hit L2)
+  auto load_round = [&](int unit, int gl, bool fetch) {
+    const int rt = unit / p.SKr, ks = unit - rt * p.SKr;
+    const int j0 = rt * kRTileRows;
+    const int ng = min(p.gpr, p.G - ks * p.gpr);
+    const __half* rowA = p.R + static_cast<size_t>(min(j0 + g, p.rank - 1)) * p.R_stride;
+    const __half* rowB = p.R + static_cast<size_t>(min(j0 + g + 8, p.rank - 1)) * p.R_stride;
+    const int kb = (ks * p.gpr + gl) * kGroup + 32 * t;
+    if (!fetch) {
+      if (gl < ng && kb + 32 <= p.IC) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(rowA + kb));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(rowB + kb));
+      }
+      return;
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int k = kb + 8 * i;
-      const bool ok = (k + 8 <= p.IC);
+      const bool ok = gl < ng && (k + 8 <= p.IC);
       a[i] = ok ? ldg_stream_v4(rowA + k) : make_uint4(0, 0, 0, 0);
       b[i] = ok ? ldg_stream_v4(rowB + k) : make_uint4(0, 0, 0, 0);
     }
-    if (dep_wait_pending) {  // R is static, x is not: the earlier kernels must be complete before x is read
-      asm volatile("griddepcontrol.wait;" ::: "memory");
-      dep_wait_pending = false;
-    }
+  };
+  // the lines of every later round of this CTA go to L2 right away; the first round is loaded for real
+  for (int unit = u0; unit < p.n_r_units; unit += ustride)
+    for (int gl = warp + (unit == u0 ? kConsumerWarps : 0); gl < p.gpr; gl += kConsumerWarps) load_round(unit, gl, false);
+  load_round(u0, warp, true);
+  int n_done = 0;
+  for (int unit = u0; unit < p.n_r_units; unit += ustride) {
+    const int rt = unit / p.SKr, ks = unit - rt * p.SKr;
+    const int gbase = ks * p.gpr, ng = min(p.gpr, p.G - gbase);
+    float acc[NT][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      const int tok = nt * 8 + g;
+    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    for (int gl = warp; gl < ng || gl == warp; gl += kConsumerWarps) {
+      const bool more_rounds = gl + kConsumerWarps < ng;
+      if (gl != warp || unit != u0) load_round(unit, gl, true);
+      if (dep_wait_pending) {  // R is static, x is not: the earlier kernels must be complete before x is read
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        dep_wait_pending = false;
+      }
+      if (gl < ng) {
+        const int kb = (gbase + gl) * kGroup + 32 * t;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int k = kb + 8 * i;
-        uint4 xv = make_uint4(0, 0, 0, 0);
-        if (tok < p.M && k + 8 <= p.IC) {
-          const __half* src = p.x + static_cast<size_t>(tok) * p.x_stride + k;
-          if (p.x_vec_ok) {
-            xv = *reinterpret_cast<const uint4*>(src);
-          } else {
-            __align__(16) __half tmp[8];
+        for (int nt = 0; nt < NT; ++nt) {
+          const int tok = nt * 8 + g;
+          // all four activation loads of the round go out before the first MMA needs one (they are L2 round trips)
+          uint4 xv[4];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) tmp[e] = src[e];
-            xv = *reinterpret_cast<const uint4*>(tmp);
+          for (int i = 0; i < 4; ++i) {
+            const int k = kb + 8 * i;
+            xv[i] = make_uint4(0, 0, 0, 0);
+            if (tok < p.M && k + 8 <= p.IC) {
+              const __half* src = p.x + static_cast<size_t>(tok) * p.x_stride + k;
+              if (p.x_vec_ok) {
+                xv[i] = ldg_cg_v4(src);
+              } else {
+                __align__(16) __half tmp[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) tmp[e] = src[e];
+                xv[i] = *reinterpret_cast<const uint4*>(tmp);
+              }
+            }
+          }
+          if (p.norm_w != nullptr && p.x_vec_ok && tok < p.M) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              if (kb + 8 * i + 8 <= p.IC) xv[i] = norm_x8(p, xv[i], tok, kb + 8 * i, s_rstd[tok]);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            mma16816(acc[nt], a[i].x, b[i].x, a[i].y, b[i].y, xv[i].x, xv[i].y);
+            mma16816(acc[nt], a[i].z, b[i].z, a[i].w, b[i].w, xv[i].z, xv[i].w);
           }
         }
-        mma16816(acc[nt], a[i].x, b[i].x, a[i].y, b[i].y, xv.x, xv.y);
-        mma16816(acc[nt], a[i].z, b[i].z, a[i].w, b[i].w, xv.z, xv.w);
       }
+      if (!more_rounds) break;
     }
+    cross_warp_reduce<NT>(acc, red, fin);  // fin[nt*128 + tok8*16 + row16]
+    float* slot = p.r_partial + static_cast<size_t>(unit) * (NT * 128);
+    for (int e = threadIdx.x; e < NT * 128; e += kConsumerThreads) slot[e] = fin[e];
+    ++n_done;
   }
-  if (dep_wait_pending) {  // (a warp without a group of its own in this unit)
+  if (dep_wait_pending) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     dep_wait_pending = false;
   }
-  cross_warp_reduce<NT>(acc, red, fin);  // fin[nt*128 + tok8*16 + row16]
-  float* slot = p.r_partial + static_cast<size_t>(unit) * (NT * 128);
-  for (int e = threadIdx.x; e < NT * 128; e += kConsumerThreads) slot[e] = fin[e];
   __threadfence();
   consumer_sync();
-  if (threadIdx.x == 0) atomicAdd(p.ws_head + WS_R_DONE, 1u);
+  if (threadIdx.x == 0) atomicAdd(p.ws_head + WS_R_DONE, static_cast<uint32_t>(n_done));
 }
 
 // Eight consecutive elements r[tok][j .. j+8) (j a multiple of 8) as four half2 registers: the SKr fp32 slots of
@@ -355,11 +463,15 @@ __device__ __forceinline__ TileInfo tile_info(const GemvParams& p, int tile, int
   return ti;
 }
 
+#ifndef GLOWQ_GEMV_MIN_CTAS
+#define GLOWQ_GEMV_MIN_CTAS 2   // CTAs per SM the register allocation is bounded for
+#endif
 template <int NT>
-__global__ void __launch_bounds__(kGemvThreads, (NT <= 2) ? 2 : 1)
+__global__ void __launch_bounds__(kGemvThreads, (NT <= 2) ? GLOWQ_GEMV_MIN_CTAS : 1)
 gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__ TensorMaps tm) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_abort;
+  __shared__ float s_rstd[8];   // fused RMSNorm: 1 / rms of every token row
   constexpr int RT = kRowTiles;
   constexpr int NB = RT * NT;  // 16-row x 8-token fragment blocks per tile
 
@@ -642,10 +754,13 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
               float o = vals[c];
               if (mb.bias) o += __half2float(mb.bias[row]);
               const size_t idx = static_cast<size_t>(tok) * mb.out_stride + row;
-              if (p.out_fp32)
+              if (p.out_fp32) {
                 static_cast<float*>(mb.out)[idx] = o;
-              else
-                static_cast<__half*>(mb.out)[idx] = __float2half_rn(o);
+              } else {
+                const __half h = __float2half_rn(o);
+                static_cast<__half*>(mb.out)[idx] = h;
+                for (int r = 0; r < p.push_world; ++r) p.push_slot[r][idx] = h;   // plain peer stores (out_stride == OC)
+              }
             }
           }
         }
@@ -657,21 +772,36 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     // ================================================================ consumer warps
     const int g = lane >> 2, t = lane & 3;
     bool dep_wait_pending = true;  // x (and a loaded r) come from earlier kernels of the stream
+    {
+      // Launch parameters live in constant memory, and the first touch of each of their cache lines is a miss of a few
+      // hundred cycles: read what the staging and the first tile need NOW, while this CTA waits for the previous kernel
+      // anyway, instead of one miss after another on the path from "x is ready" to the first MMA.
+      const int t0 = tile_at(0);
+      const TileInfo tf = tile_info(p, t0 < p.n_tiles ? t0 : 0, slice);
+      const MemberDev& m0 = p.mem[tf.mi];
+      asm volatile("" ::"r"(m0.OC), "r"(m0.out_stride), "f"(m0.alpha), "l"(m0.bias), "l"(m0.out), "l"(m0.L), "r"(p.M),
+                   "r"(p.xs_stride), "r"(p.rank), "r"(p.r_mode), "l"(p.x), "r"(p.x_stride), "r"(p.IC), "r"(p.x_vec_ok),
+                   "r"(p.SK), "r"(p.out_fp32), "r"(p.push_world), "l"(p.norm_w));
+    }
+    if (p.norm_w != nullptr) {     // the row statistics come first: both the R units and the staging need them
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      dep_wait_pending = false;
+      norm_stats(p, red, s_rstd);
+    }
     if (r_only) {
       // The grid is persistent - never larger than what is resident at once - so every unit's owner is running
       // while the other CTAs wait (bounded) for r before their first L epilogue.  R loads go out before the
       // dependency wait; x is staged only afterwards, for the row tiles this CTA picks up later.
-      for (int u = static_cast<int>(blockIdx.x) - n_main; u < p.n_r_units; u += p.n_r_ctas)
-        r_unit<NT>(p, u, red, fin, dep_wait_pending);
+      r_units<NT>(p, static_cast<int>(blockIdx.x) - n_main, p.n_r_ctas, red, fin, dep_wait_pending, s_rstd);
     } else if (p.r_mode == 1 && p.n_r_ctas == 0) {
-      // a large right factor: every CTA takes its share of R units (dealt from the last CTA down) before its tiles
-      for (int u = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x); u < p.n_r_units; u += gridDim.x)
-        r_unit<NT>(p, u, red, fin, dep_wait_pending);
+      // no dedicated CTAs: every CTA takes its share of R units (dealt from the last CTA down) before its tiles
+      r_units<NT>(p, static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), red, fin,
+                  dep_wait_pending, s_rstd);
     }
     if (threadIdx.x == 0 && r_only) trace_event(p, 6);
     if (dep_wait_pending) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x == 0) trace_event(p, 2);
-    if (!r_only || deal_all) stage_x(p, g0, ng, xs, xsum, 8 * NT);
+    if (!r_only || deal_all) stage_x(p, g0, ng, xs, xsum, 8 * NT, s_rstd);
     if (threadIdx.x < kZeroRowBytes / 4) reinterpret_cast<uint32_t*>(zero_row)[threadIdx.x] = 0u;
     consumer_sync();  // publishes xs / xsum / the zero row
     if (threadIdx.x == 0) trace_event(p, 3);
@@ -719,11 +849,11 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
         if (ok && c * kChunkGroups + warp < ng && !(tuning_bits(p) & 1)) {
           const uint32_t wbase = ring_lane + st * kStageBytes;
           uint4 W[RT][2];
-#pragma unroll
-          for (int j = 0; j < RT; ++j) {
-            W[j][0] = lds128(wbase + (j * 16) * kRowPitch);
-            W[j][1] = lds128(wbase + (j * 16 + 8) * kRowPitch);
-          }
+          static_assert(RT == 2, "row-tile offsets below are written out for two row tiles");
+          W[0][0] = lds128_at<0>(wbase);
+          W[0][1] = lds128_at<8 * kRowPitch>(wbase);
+          W[1][0] = lds128_at<16 * kRowPitch>(wbase);
+          W[1][1] = lds128_at<24 * kRowPitch>(wbase);
           float ag[RT][NT][4];
 #pragma unroll
           for (int j = 0; j < RT; ++j)
@@ -734,7 +864,9 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
             constexpr uint32_t MLO = 0x000F000Fu, MHI = 0x00F000F0u;
             uint4 xb[NT];
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) xb[nt] = lds128(xa[nt] + i * 64);
+            for (int nt = 0; nt < NT; ++nt)
+              xb[nt] = (i == 0) ? lds128_at<0>(xa[nt]) : (i == 1) ? lds128_at<64>(xa[nt]) : (i == 2) ? lds128_at<128>(xa[nt])
+                                                                                                     : lds128_at<192>(xa[nt]);
 #pragma unroll
             for (int j = 0; j < RT; ++j) {
               const uint32_t a = (i == 0) ? W[j][0].x : (i == 1) ? W[j][0].y : (i == 2) ? W[j][0].z : W[j][0].w;
@@ -750,7 +882,9 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
           // group epilogue: rows g, g+8 (row tile 0), g+16, g+24 (row tile 1) of this warp's group
 #pragma unroll
           for (int j = 0; j < RT; ++j) {
-            const float2 pA = lds_f2(ck + (j * 16) * 8), pB = lds_f2(ck + (j * 16 + 8) * 8);  // {s * 2^24, -s * z}
+            // {s * 2^24, -s * z} of rows g, g + 8 of row tile j
+            const float2 pA = (j == 0) ? lds_f2_at<0>(ck) : lds_f2_at<128>(ck);
+            const float2 pB = (j == 0) ? lds_f2_at<64>(ck) : lds_f2_at<192>(ck);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
               const float2 xs2 = lds_f2(xsu + nt * 32);
@@ -860,10 +994,13 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
             for (int w = 0; w < kConsumerWarps; ++w) o += redb[((w * NB + b) * 32 + ln) * 4 + cc];
             if (mb.bias) o += __half2float(mb.bias[row]);
             const size_t idx = static_cast<size_t>(tok) * mb.out_stride + row;
-            if (p.out_fp32)
+            if (p.out_fp32) {
               static_cast<float*>(mb.out)[idx] = o;
-            else
-              static_cast<__half*>(mb.out)[idx] = __float2half_rn(o);
+            } else {
+              const __half h = __float2half_rn(o);
+              static_cast<__half*>(mb.out)[idx] = h;
+              for (int r = 0; r < p.push_world; ++r) p.push_slot[r][idx] = h;
+            }
           }
         }
         break;
@@ -891,12 +1028,22 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
 
   __syncthreads();
   if (threadIdx.x == 0) trace_event(p, 10);
-  if (p.r_mode == 1 && threadIdx.x == 0) {
+  if ((p.r_mode == 1 || p.push_world > 0) && threadIdx.x == 0) {
+    if (p.push_world > 0) __threadfence_system();   // this CTA's peer stores are ordered before the flags below
     const uint32_t old = atomicAdd(p.ws_head + WS_EXIT, 1u);
     if (old == gridDim.x - 1) {  // last CTA out re-arms the counters for the next launch
       p.ws_head[WS_R_DONE] = 0u;
       p.ws_head[WS_EXIT] = 0u;
       __threadfence();
+      if (p.push_world > 0) {
+        // every CTA's stores are out: publish this call's epoch on every rank (the finishing kernel of each rank waits
+        // for all sources' flags of the site to reach its own epoch)
+        const uint32_t e = *p.push_epoch + 1u;
+        *p.push_epoch = e;
+        __threadfence_system();
+        for (int r = 0; r < p.push_world; ++r)
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.push_flag[r]), "r"(e) : "memory");
+      }
     }
   }
 }

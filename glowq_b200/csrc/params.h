@@ -44,6 +44,7 @@ enum : int { WS_TICKET = 0, WS_R_DONE = 1, WS_EXIT = 2, WS_STATUS = 3, WS_HEADER
 constexpr size_t kWsHeaderBytes = WS_HEADER_WORDS * 4;
 constexpr int kMaxRTiles = 64;      // rank <= 1024
 constexpr int kMaxPrefetch = kMaxMembers + 1;
+constexpr int kMaxRanks = 8;        // GLOWQ_MAX_RANKS
 constexpr unsigned kPrefetchSlice = 16u << 10;  // bytes per L2 prefetch request
 
 struct MemberDev {
@@ -91,6 +92,18 @@ struct GemvParams {
   int n_pf;
   const unsigned char* pf_ptr[kMaxPrefetch];
   unsigned pf_bytes[kMaxPrefetch];
+  // Tensor-parallel push (row-split linears): push_slot[r] = rank r's staging slot for THIS rank's partial result
+  // ([M][OC] fp16, dense), push_flag[r] = the epoch flag this rank releases on rank r, push_epoch = local call counter
+  // of the site.  push_world == 0: no push.
+  // fused residual add + RMSNorm of the activations (norm_w == nullptr: none)
+  const __half* norm_w;
+  const __half* residual;
+  __half* hidden_out;
+  float norm_eps;
+  int push_world;
+  __half* push_slot[kMaxRanks];
+  uint32_t* push_flag[kMaxRanks];
+  uint32_t* push_epoch;
   MemberDev mem[kMaxMembers];
 };
 

@@ -7,6 +7,8 @@
 // Sums are bit-identical on all ranks (same order).  No NCCL call, so a whole token step including its collectives
 // can be replayed from one CUDA graph; no peer LOADS, no multicast, no multimem.  The ranks' kernels run on
 // different GPUs; a rank that never arrives makes the others record a status word and return.
+#include <cstdlib>
+
 #include "../../include/glowq_w4a16.h"
 #include "common.cuh"
 #include "params.h"
@@ -17,6 +19,17 @@ namespace {
 constexpr int kArThreads = 512;
 constexpr unsigned kArSpinLimit = 1u << 22;
 
+// Polls a rank makes on a peer's flag before it gives up (status 4).  GLOWQ_AR_SPIN_LIMIT shortens it, for tests of
+// the expiry path; read once.
+unsigned ar_spin_limit() {
+  static const unsigned v = [] {
+    const char* e = std::getenv("GLOWQ_AR_SPIN_LIMIT");
+    const long n = (e && *e) ? std::atol(e) : 0;
+    return n > 0 ? static_cast<unsigned>(n) : kArSpinLimit;
+  }();
+  return v;
+}
+
 struct ArParams {
   unsigned char* buf[GLOWQ_MAX_RANKS];   // staging buffer of every rank: [sites][world][max_n] fp16
   uint32_t* flag[GLOWQ_MAX_RANKS];       // epoch flags of every rank: [sites][world]
@@ -24,6 +37,8 @@ struct ArParams {
   uint32_t* status;                      // local status word
   __half* inout;                         // local vector, n halves (n % 8 == 0, 16-byte aligned)
   int world, rank, site, n, max_n;
+  unsigned spin_limit;
+  int finish_only;                       // the partial results were pushed by the producing launch: wait and sum only
 };
 
 __global__ void __launch_bounds__(kArThreads) allreduce_push_kernel(const __grid_constant__ ArParams p) {
@@ -31,23 +46,26 @@ __global__ void __launch_bounds__(kArThreads) allreduce_push_kernel(const __grid
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");   // the partial sums come from the previous kernel
   if (threadIdx.x == 0) {
-    s_epoch = p.epoch[p.site] + 1;
-    p.epoch[p.site] = s_epoch;
+    // finish only: the pushing launch (complete by now) advanced the site's epoch and released the flags itself
+    s_epoch = p.finish_only ? p.epoch[p.site] : p.epoch[p.site] + 1;
+    if (!p.finish_only) p.epoch[p.site] = s_epoch;
   }
   __syncthreads();
   const uint32_t e = s_epoch;
   const int nv = p.n >> 3;  // 16-byte vectors
-  const size_t slot = (static_cast<size_t>(p.site) * p.world + p.rank) * p.max_n * sizeof(__half);
-  const uint4* src = reinterpret_cast<const uint4*>(p.inout);
-  for (int i = threadIdx.x; i < nv; i += kArThreads) {
-    const uint4 v = src[i];
-    for (int r = 0; r < p.world; ++r) reinterpret_cast<uint4*>(p.buf[r] + slot)[i] = v;
-  }
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x < p.world) {
-    uint32_t* f = p.flag[threadIdx.x] + p.site * p.world + p.rank;
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(e) : "memory");
+  if (!p.finish_only) {
+    const size_t slot = (static_cast<size_t>(p.site) * p.world + p.rank) * p.max_n * sizeof(__half);
+    const uint4* src = reinterpret_cast<const uint4*>(p.inout);
+    for (int i = threadIdx.x; i < nv; i += kArThreads) {
+      const uint4 v = src[i];
+      for (int r = 0; r < p.world; ++r) reinterpret_cast<uint4*>(p.buf[r] + slot)[i] = v;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < p.world) {
+      uint32_t* f = p.flag[threadIdx.x] + p.site * p.world + p.rank;
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(e) : "memory");
+    }
   }
   if (threadIdx.x < p.world) {
     const uint32_t* f = p.flag[p.rank] + p.site * p.world + threadIdx.x;
@@ -56,7 +74,7 @@ __global__ void __launch_bounds__(kArThreads) allreduce_push_kernel(const __grid
       uint32_t v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
       if (static_cast<int32_t>(v - e) >= 0) break;
-      if (++spins > kArSpinLimit) {
+      if (++spins > p.spin_limit) {
         atomicExch(p.status, 4u);
         break;
       }
@@ -90,7 +108,8 @@ __global__ void __launch_bounds__(kArThreads) allreduce_push_kernel(const __grid
 }  // namespace
 }  // namespace glowq
 
-extern "C" int glowq_w4a16_allreduce_f16(const glowq_w4a16_peers_t* peers, void* inout, int n, int site, void* stream) {
+namespace {
+int launch_allreduce(const glowq_w4a16_peers_t* peers, void* inout, int n, int site, void* stream, int finish_only) {
   using namespace glowq;
   if (!peers || !inout || n <= 0 || site < 0) return GLOWQ_ERR_BAD_ARGUMENT;
   if (peers->world < 1 || peers->world > GLOWQ_MAX_RANKS || peers->rank < 0 || peers->rank >= peers->world)
@@ -112,6 +131,8 @@ extern "C" int glowq_w4a16_allreduce_f16(const glowq_w4a16_peers_t* peers, void*
   p.site = site;
   p.n = n;
   p.max_n = peers->max_n;
+  p.spin_limit = ar_spin_limit();
+  p.finish_only = finish_only;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(1);
   cfg.blockDim = dim3(kArThreads);
@@ -123,4 +144,13 @@ extern "C" int glowq_w4a16_allreduce_f16(const glowq_w4a16_peers_t* peers, void*
   cfg.numAttrs = 1;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, allreduce_push_kernel, p);
   return e == cudaSuccess ? GLOWQ_OK : GLOWQ_ERR_CUDA;
+}
+}  // namespace
+
+extern "C" int glowq_w4a16_allreduce_f16(const glowq_w4a16_peers_t* peers, void* inout, int n, int site, void* stream) {
+  return launch_allreduce(peers, inout, n, site, stream, 0);
+}
+
+extern "C" int glowq_w4a16_allreduce_finish_f16(const glowq_w4a16_peers_t* peers, void* out, int n, int site, void* stream) {
+  return launch_allreduce(peers, out, n, site, stream, 1);
 }

@@ -39,6 +39,10 @@ class Group(ctypes.Structure):
                 ("r_mode", ctypes.c_int32), ("out_dtype", ctypes.c_int32), ("kernel", ctypes.c_int32),
                 ("n_members", ctypes.c_int32), ("split_k", ctypes.c_int32), ("reserved", ctypes.c_int32),
                 ("next", ctypes.c_void_p),     # address of the Group that follows on the stream, or None
+                ("push", ctypes.c_void_p),     # address of a Peers struct: push the result to every rank (row-split TP)
+                ("push_site", ctypes.c_int32), ("reserved2", ctypes.c_int32),
+                ("norm_weight", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("hidden_out", ctypes.c_void_p),
+                ("norm_eps", ctypes.c_float), ("reserved3", ctypes.c_int32),
                 ("members", Member * MAX_MEMBERS)]
 
 
@@ -54,7 +58,8 @@ class Peers(ctypes.Structure):
 EXPORTS = ("glowq_w4a16_version", "glowq_w4a16_strerror", "glowq_w4a16_last_cuda_error", "glowq_w4a16_dequant",
            "glowq_w4a16_gemv_forward", "glowq_w4a16_gemm_forward", "glowq_w4a16_group_forward",
            "glowq_w4a16_group_forward_many", "glowq_w4a16_group_forward_host", "glowq_w4a16_workspace_bytes",
-           "glowq_w4a16_read_status", "glowq_w4a16_gemv_forward_static", "glowq_w4a16_allreduce_f16")
+           "glowq_w4a16_read_status", "glowq_w4a16_gemv_forward_static", "glowq_w4a16_allreduce_f16",
+           "glowq_w4a16_allreduce_finish_f16")
 
 
 def library_path() -> str:
@@ -90,6 +95,7 @@ class _Ext:
         lib.glowq_w4a16_read_status.argtypes = [vp, vp]
         lib.glowq_w4a16_gemv_forward_static.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]
         lib.glowq_w4a16_allreduce_f16.argtypes = [ctypes.POINTER(Peers), vp, i32, i32, vp]
+        lib.glowq_w4a16_allreduce_finish_f16.argtypes = [ctypes.POINTER(Peers), vp, i32, i32, vp]
         if lib.glowq_w4a16_version() != ABI_VERSION:
             raise RuntimeError("libglowq_w4a16.so ABI version mismatch; rebuild with `python -m glowq_b200.build`")
         self._ws = {}

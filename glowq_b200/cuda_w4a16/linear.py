@@ -181,8 +181,11 @@ class CudaW4A16Linear(nn.Module):
             self._ws_key = key
         return self._ws
 
-    def launch(self, x2d: torch.Tensor, *, L=None, R=None, r_buf=None, r_mode=K.R_NONE, alpha=0.0) -> torch.Tensor:
-        """One library call: this linear, optionally with its low-rank correction folded in."""
+    def launch(self, x2d: torch.Tensor, *, L=None, R=None, r_buf=None, r_mode=K.R_NONE, alpha=0.0, push=None,
+               push_site: int = 0) -> torch.Tensor:
+        """One library call: this linear, optionally with its low-rank correction folded in.  ``push``: a
+        ``glowq_b200.tp.PeerAllReduce`` - a row-split tensor-parallel shard then also stores its result into every
+        rank's staging slot of ``push_site`` (complete the sum with ``push.finish(out, push_site)``)."""
         ext = self._get_ext()
         m = x2d.size(0)
         out = torch.empty((m, self.out_features), dtype=self._out_dtype, device=x2d.device)
@@ -201,6 +204,8 @@ class CudaW4A16Linear(nn.Module):
         grp.out_dtype = K.OUT_F32 if self._out_dtype == torch.float32 else K.OUT_F16
         grp.kernel = self.kernel_choice(m)
         grp.n_members = 1
+        if push is not None:
+            grp.push, grp.push_site = push.descriptor_address(), int(push_site)
         self.fill_member(grp.members[0], out, L if r_mode != K.R_NONE else None, alpha)
         with torch.cuda.device(x2d.device):
             ws = self.workspace_for(m, rank, x2d.device)

@@ -201,9 +201,11 @@ class LinearStack:
 
     # ------------------------------------------------------------------ launch plans
     def plan(self, M: int, *, corrected: bool = True, fuse_groups: bool = True, kernel: int = K.KERNEL_AUTO,
-             out_dtype: int = K.OUT_F16, split_k: int = 0, chain: bool = True):
+             out_dtype: int = K.OUT_F16, split_k: int = 0, chain: bool = True, push=None):
         """Build (once per configuration) the ctypes array of group calls for one token step of M tokens."""
-        key = (M, corrected, fuse_groups, kernel, out_dtype, split_k, chain)
+        # push: a glowq_b200.tp.PeerAllReduce - the row-split groups (o_proj, down_proj) then store their partial result
+        # into every rank's staging slot themselves (sites alternate), to be completed by push.finish(out, site)
+        key = (M, corrected, fuse_groups, kernel, out_dtype, split_k, chain, id(push))
         if key in self._plans:
             return self._plans[key]
         s = self.shape
@@ -219,6 +221,7 @@ class LinearStack:
         calls = []
         keep = [inputs]
         group_outs = []
+        n_row_split = 0
         stream = torch.cuda.current_stream(self.device).cuda_stream
         for g in self.groups:
             outs = [torch.empty(M, m.oc, dtype=dt, device=self.device) for m in g.members]
@@ -252,6 +255,10 @@ class LinearStack:
                     mem.scale_stride = m.scales.stride(0)
                     mem.alpha = 1.0
                 off += len(ms)
+                if push is not None and g.input_name in ("attn", "inter") and len(ms) == 1 and M <= 8 \
+                        and out_dtype == K.OUT_F16:
+                    c.push, c.push_site = push.descriptor_address(), n_row_split & 1
+                    n_row_split += 1
                 c.workspace, c.workspace_bytes, c.stream = ws.data_ptr(), ws.numel(), stream
                 calls.append(c)
                 keep.append(ws)

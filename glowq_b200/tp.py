@@ -136,5 +136,20 @@ class PeerAllReduce:
         self.ext.check(rc, "glowq_w4a16_allreduce_f16")
         return t
 
+    def descriptor_address(self) -> int:
+        """Address of the ``glowq_w4a16_peers_t`` (for ``Group.push``: the row-split launch stores its result into every
+        rank's slot itself; complete with :meth:`finish`)."""
+        import ctypes
+        return ctypes.addressof(self.peers)
+
+    def finish(self, out: torch.Tensor, site: int) -> torch.Tensor:
+        """Second half after a pushing launch on ``site``: wait for every rank's flag and write the sum to ``out``."""
+        if out.dtype != torch.float16 or not out.is_contiguous() or out.numel() % 8:
+            raise ValueError("expected a contiguous fp16 tensor with a multiple of 8 elements")
+        rc = self.ext.lib.glowq_w4a16_allreduce_finish_f16(self.peers, out.data_ptr(), out.numel(), int(site),
+                                                           torch.cuda.current_stream(out.device).cuda_stream)
+        self.ext.check(rc, "glowq_w4a16_allreduce_finish_f16")
+        return out
+
     def status(self) -> int:
         return int(self.local[32].item())

@@ -104,6 +104,28 @@ typedef struct glowq_w4a16_group {
    * Nothing is computed for `next`, and a wrong hint costs bandwidth, not correctness.  The reference has
    * no counterpart (its launches are independent: csrc/gemv_w4a16.cu:194-211). */
   const struct glowq_w4a16_group* next;
+  /* Optional, tensor-parallel row-split linears (o_proj, down_proj shards): besides writing `out`, the launch stores
+   * its result - this rank's partial sum - into slot [push_site][rank] of EVERY rank's staging buffer as its tiles
+   * finish, and releases the per-(site, rank) epoch flags once the whole launch is complete: the first half of
+   * glowq_w4a16_allreduce_f16 without a launch of its own.  glowq_w4a16_allreduce_finish_f16 (same peers, same site)
+   * waits for all ranks' flags and adds the slots.  Requirements: one member, fp16 output, out_stride == OC,
+   * M * OC <= peers->max_n and a multiple of 8, M <= 8 (the weight-streaming kernel); GLOWQ_ERR_UNSUPPORTED_SHAPE
+   * otherwise.  NULL = no push.  See glowq_w4a16_peers_t below for the buffers. */
+  const struct glowq_w4a16_peers* push;
+  int32_t push_site;
+  int32_t reserved2;      /* must be 0 */
+  /* Optional input transform fused into the activation staging (the residual add and RMSNorm that sit in front of
+   * q/k/v and gate/up in Llama / Qwen decoder blocks; the reference runs them as separate PyTorch modules of the model):
+   *     h  = fp16(x + residual)                                  (residual NULL: h = x)
+   *     xn = norm_weight * fp16(h * rsqrt(mean_k(h^2) + norm_eps))   (statistics in fp32, per token)
+   * and the linears (and r = R . xn) consume xn.  hidden_out, if not NULL, receives h ([M, x_stride] fp16: the new
+   * residual stream).  norm_weight NULL = no transform.  Requirements: weight-streaming kernel (M <= 8), IC a multiple
+   * of 8, x / residual / norm_weight / hidden_out 16-byte aligned rows; GLOWQ_ERR_UNSUPPORTED_SHAPE otherwise. */
+  const void* norm_weight; /* fp16 [IC]                                                        */
+  const void* residual;    /* fp16 [M, x_stride] or NULL                                       */
+  void* hidden_out;        /* fp16 [M, x_stride] or NULL                                       */
+  float norm_eps;
+  int32_t reserved3;       /* must be 0 */
   glowq_w4a16_member_t members[GLOWQ_MAX_MEMBERS];
 } glowq_w4a16_group_t;
 
@@ -194,6 +216,12 @@ typedef struct glowq_w4a16_peers {
   int32_t world, rank, sites, max_n;
 } glowq_w4a16_peers_t;
 int glowq_w4a16_allreduce_f16(const glowq_w4a16_peers_t* peers, void* inout, int n, int site, void* stream);
+
+/* Second half of the all-reduce for a launch that pushed its result itself (glowq_w4a16_group_t.push): wait - bounded,
+ * status 4 on expiry - until every rank's flag of `site` carries the epoch of this rank's latest push on that site,
+ * add the `world` slots of the local staging buffer in rank order (fp32) and write the n fp16 sums to `out`.  Every
+ * rank calls it after its pushing launch, on the same stream; the sums are bit-identical on all ranks. */
+int glowq_w4a16_allreduce_finish_f16(const glowq_w4a16_peers_t* peers, void* out, int n, int site, void* stream);
 
 /* Bytes of workspace a group call with these sizes needs (sync words + split-K partial sums). */
 size_t glowq_w4a16_workspace_bytes(int M, int IC, int OC_total, int rank, int n_members);

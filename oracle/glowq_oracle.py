@@ -176,6 +176,23 @@ class GroupCacheModel:
         return "compute"
 
 
+def residual_rmsnorm_f16(x_f16, residual_f16, weight_f16, eps: float):
+    """The residual add and RMSNorm that precede q/k/v and gate/up in a Llama / Qwen decoder block, as the model code
+    the reference runs computes them (the reference itself has no norm code: it evaluates HF models, whose
+    ``LlamaRMSNorm.forward`` - transformers models/llama/modeling_llama.py - and decoder layer do exactly this):
+        h  = residual + x                          fp16 add (one rounding)
+        xn = weight * (h.float() * rsqrt(mean(h.float()^2) + eps)).half()      fp16 product (one more rounding)
+    Returns (xn fp16, h fp16)."""
+    x = np.asarray(x_f16, dtype=np.float16)
+    h = x if residual_f16 is None else (x.astype(np.float32) + np.asarray(residual_f16, np.float16).astype(np.float32)
+                                        ).astype(np.float16)
+    hf = h.astype(np.float32)
+    var = np.mean(hf * hf, axis=-1, keepdims=True, dtype=np.float32)
+    n = (hf * (1.0 / np.sqrt(var + np.float32(eps))).astype(np.float32)).astype(np.float16)
+    xn = (np.asarray(weight_f16, np.float16).astype(np.float32) * n.astype(np.float32)).astype(np.float16)
+    return xn, h
+
+
 def parity_errors(y, y_ref):
     """(max-abs error, mean-rel error) with mean-rel = mean|y - y_ref| / mean|y_ref|."""
     y = np.asarray(y, dtype=np.float64)

@@ -209,6 +209,40 @@ def test_counters_rearm_over_many_launches():
     assert_close(out, lin.oracle(x, R))
 
 
+@pytest.mark.parametrize("ocs,ic,rank,M,with_res", [([512, 128, 128], 1024, 64, 1, True), ([512, 128, 128], 1024, 64, 5, False),
+                                                   ([256], 8192, 32, 2, True), ([3072, 1024, 1024], 3072, 64, 1, True)])
+def test_fused_residual_rmsnorm_prologue(ocs, ic, rank, M, with_res):
+    """The launch stages xn = w * fp16(rstd * fp16(x + residual)) instead of x (and hands h = x + residual back): every
+    member's output and r against the oracle evaluated on the oracle's own xn; h bit for bit.  The long-K case runs
+    K-sliced, where every slice needs the statistics of the whole row."""
+    rng = np.random.default_rng(ic + M)
+    lins = [Linear(rng, oc, ic, rank=rank) for oc in ocs]
+    R = (rng.standard_normal((rank, ic)) * 0.01).astype(np.float16)
+    x = rng.standard_normal((M, ic)).astype(np.float16)
+    res = (rng.standard_normal((M, ic)) * 2).astype(np.float16) if with_res else None
+    w = (1 + 0.2 * rng.standard_normal(ic)).astype(np.float16)
+    xn, h = O.residual_rmsnorm_f16(x, res, w, 1e-5)
+    outs = [new_out(M, l) for l in lins]
+    r_buf = torch.zeros(M, rank, dtype=torch.float16, device="cuda")
+    g = make_group(dev(x), lins, outs, R_d=dev(R), r_buf=r_buf, r_mode=K.R_COMPUTE)
+    w_d, res_d = dev(w), (dev(res) if with_res else None)
+    h_d = torch.zeros(M, ic, dtype=torch.float16, device="cuda")
+    g.norm_weight, g.norm_eps, g.hidden_out = w_d.data_ptr(), 1e-5, h_d.data_ptr()
+    g.residual = res_d.data_ptr() if with_res else None
+    for _ in range(2):
+        assert run_group(g) == 0 and status_ok(g) == 0
+    np.testing.assert_array_equal(h_d.cpu().numpy().view(np.uint16), h.view(np.uint16))
+    for l, o in zip(lins, outs):
+        assert_close(o, l.oracle(xn, R), tag=f"norm {l.oc}x{l.ic} M={M}")
+    r_want = xn.astype(np.float32) @ R.astype(np.float32).T
+    assert np.abs(r_buf.float().cpu().numpy() - r_want).max() <= 6e-3
+    # more than 8 tokens or the tensor-core kernel: refused, nothing runs
+    g.kernel = K.KERNEL_GEMM
+    assert ext().lib.glowq_w4a16_group_forward(g) == 8
+    g.kernel, g.norm_weight = K.KERNEL_AUTO, None
+    assert ext().lib.glowq_w4a16_group_forward(g) == 1          # residual / hidden_out without a norm weight
+
+
 # ---------------------------------------------------------------------------------------------- tensor-core GEMM
 @pytest.mark.parametrize("M,oc,ic,rank,alpha,bias", [
     (64, 256, 512, 0, 1.0, False), (128, 128, 128, 0, 1.0, False), (200, 136, 1152, 0, 1.0, True),

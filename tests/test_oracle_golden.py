@@ -100,3 +100,24 @@ def test_c_oracle_matches_numpy(golden_forward, golden_quant):
                                   alpha=0.5, r_io=r_io, r_mode=1 if i == 0 else 2)
         ma, mr = O.parity_errors(got, want)
         assert ma < 1e-4 and mr < 1e-5, (n, ma, mr)
+
+
+def test_residual_rmsnorm_matches_the_model_code():
+    """The oracle's residual add + RMSNorm against the module the reference's model code runs (HF LlamaRMSNorm on
+    CPU, fp16 in / fp16 out), bit for bit up to the last-place differences of the fp32 mean."""
+    import torch
+    from transformers.models.llama.modeling_llama import LlamaRMSNorm
+    rng = np.random.default_rng(21)
+    for M, d in ((1, 256), (5, 3072)):
+        x = rng.standard_normal((M, d)).astype(np.float16)
+        res = (rng.standard_normal((M, d)) * 3).astype(np.float16)
+        w = (1 + 0.1 * rng.standard_normal(d)).astype(np.float16)
+        norm = LlamaRMSNorm(d, eps=1e-5)
+        norm.weight.data = torch.from_numpy(w.copy())
+        h_t = torch.from_numpy(res.copy()) + torch.from_numpy(x.copy())
+        want = norm(h_t).detach().numpy()
+        got, h = O.residual_rmsnorm_f16(x, res, w, 1e-5)
+        assert np.array_equal(h.view(np.uint16), h_t.numpy().view(np.uint16))
+        diff = np.abs(got.astype(np.float32) - want.astype(np.float32))
+        assert (diff <= np.abs(want.astype(np.float32)) * 2 ** -9 + 1e-7).all()       # at most one fp16 ulp
+        assert (got.view(np.uint16) != want.view(np.uint16)).mean() < 0.02

@@ -81,6 +81,16 @@ def _worker(rank, world, port, q):
             y = down_sh.launch(h_sh, L=L_down, R=R_down_sh, r_buf=r_buf2, r_mode=K.R_COMPUTE, alpha=1.0)
             ar.all_reduce(y)
             torch.cuda.synchronize()
+            # the same sum with the partial result pushed to the peers by the row-split launch itself (M <= 8)
+            y_push = None
+            if M <= 8:
+                for rep in range(3):          # sites alternate; the epochs advance on every call
+                    r_buf3 = torch.zeros(M, RANK, dtype=torch.float16, device=dev)
+                    y_push = down_sh.launch(h_sh, L=L_down, R=R_down_sh, r_buf=r_buf3, r_mode=K.R_COMPUTE, alpha=1.0,
+                                            push=ar, push_site=rep & 1)
+                    ar.finish(y_push, site=rep & 1)
+                    torch.cuda.synchronize()
+                assert torch.equal(y_push, y), "pushed sum differs from the all-reduce kernel's"
             # gather the sharded h (NCCL, test plumbing only) so that the oracle of down_proj sees the same input
             parts = [torch.empty(M, b - a, dtype=torch.float16, device=dev) for a, b in tp.row_bounds(INTER, world, 128)]
             for r in range(world):

@@ -83,3 +83,37 @@ def test_peer_allreduce_matches_nccl():
     for rank, worst, status in res:
         assert status == 0, (rank, status)
         assert worst <= 2e-2, (rank, worst)       # fp16 rounding of a sum of two O(1) values
+
+
+_EXPIRY_SCRIPT = r"""
+import ctypes, sys, torch
+from glowq_b200.cuda_w4a16 import kernels as K
+ext = K.load_w4a16_extension()
+dev = torch.device("cuda", 0)
+world, sites, max_n = 2, 2, 1024
+mem = [torch.zeros(sites * world * max_n, dtype=torch.float16, device=dev) for _ in range(world)]
+flags = [torch.zeros(sites * world, dtype=torch.int32, device=dev) for _ in range(world)]
+local = torch.zeros(64, dtype=torch.int32, device=dev)
+p = K.Peers()
+for r in range(world):                       # "rank 1" is local memory that nobody ever writes flags into
+    p.buf[r], p.flag[r] = mem[r].data_ptr(), flags[r].data_ptr()
+p.epoch, p.status = local.data_ptr(), local.data_ptr() + 32 * 4
+p.world, p.rank, p.sites, p.max_n = world, 0, sites, max_n
+x = torch.ones(1024, dtype=torch.float16, device=dev)
+rc = ext.lib.glowq_w4a16_allreduce_f16(p, x.data_ptr(), 1024, 0, torch.cuda.current_stream().cuda_stream)
+torch.cuda.synchronize()                     # the kernel returned although rank 1 never arrived
+print("RC", rc, "STATUS", int(local[32].item()), "FLAG0", int(flags[0][0].item()), "FLAG1", int(flags[1][0].item()))
+"""
+
+
+def test_bounded_wait_runs_out_when_a_rank_never_arrives():
+    """One GPU: a two-rank descriptor whose second rank is plain local memory that nobody launches for.  With the poll
+    limit set short (read once per process, hence the child interpreter) the kernel gives up, records status 4 and
+    returns; the context stays usable."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, GLOWQ_AR_SPIN_LIMIT="2000", PYTHONPATH=root)
+    r = subprocess.run([sys.executable, "-c", _EXPIRY_SCRIPT], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "RC 0 STATUS 4 FLAG0 1 FLAG1 1" in r.stdout, r.stdout[-2000:]
