@@ -662,7 +662,7 @@ def run_sweep(arm, args, main_stack=None):
         stack._plans.clear()
         return {"model": shape.name, "batch": M, "glowq_s_fraction": fraction, "ms_per_step": ms,
                 "tokens_per_s": M / (ms * 1e-3), "GBs": alg / (ms * 1e-3) / 1e9, "frac_of_measured_hbm": alg / (ms * 1e-3) / 1e9 / peak,
-                "tflops": fl / (ms * 1e-3) / 1e12, "kernel": "gemv_stream" if M <= 16 else "gemm_tcgen05",
+                "tflops": fl / (ms * 1e-3) / 1e12, "kernel": "gemv_stream" if M <= 8 else "gemm_tcgen05",
                 "launches": plan["n"]}
 
     for name, batches, fraction in (("llama-3.2-3b", (1, 8, 32), 1.0), ("qwen2.5-7b", (1, 64), 0.5),
@@ -684,7 +684,7 @@ def run_sweep(arm, args, main_stack=None):
         fl = stack.algorithmic_flops(M, corrected=True) / 2
         us = ms * 1e3 / 2
         out["qwen3_14b_m_sweep"].append({"M": M, "us_per_layer": us, "GBs": alg / us / 1e3, "tflops": fl / us / 1e6,
-                                         "kernel": "gemv_stream" if M <= 16 else "gemm_tcgen05"})
+                                         "kernel": "gemv_stream" if M <= 8 else "gemm_tcgen05"})
         stack._plans.clear()
         torch.cuda.empty_cache()
     del stack

@@ -142,7 +142,7 @@ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 constexpr int kGemvMaxM = 8;                  // tokens per launch of the weight-streaming kernel (one MMA N tile)
-constexpr int kGemvAutoMaxM = 16;             // GLOWQ_KERNEL_AUTO: up to two such launches, the tensor-core GEMM above
+constexpr int kGemvAutoMaxM = 8;              // GLOWQ_KERNEL_AUTO: one such launch, the tensor-core GEMM above
 constexpr size_t kSmemTwoPerSm = 112 * 1024;  // dynamic shared memory that still lets two CTAs share an SM
 constexpr size_t kSmemOnePerSm = 224 * 1024;
 
@@ -532,10 +532,9 @@ int glowq_w4a16_group_forward(const glowq_w4a16_group_t* group) {
   if (rc != GLOWQ_OK) return rc;
   if (g.M == 0) return GLOWQ_OK;
   cudaStream_t stream = static_cast<cudaStream_t>(g.stream);
-  // Measured on B200: 8 tokens stream at the cost of one, so M tokens cost ceil(M/8) streaming launches.  The tcgen05
-  // GEMM (K-sliced over all SMs when it has few tiles) takes about the same time for anything up to 128 tokens.  At
-  // 16 tokens (two streaming launches) the two are level (Llama-3.2-3B q/k/v: 20 vs 17 us plain, 26 vs 26 corrected;
-  // gate/up: 30 vs 30); from 17 tokens (three launches) the GEMM wins everywhere.
+  // Measured on B200: up to 8 tokens fit one streaming launch (one MMA N tile); 9..16 tokens would take two, and at
+  // 16 tokens the tcgen05 GEMM (K-sliced over all SMs when it has few tiles) is ahead on every Llama-2-13B shape
+  // (q/k/v 44 vs 47 us, gate/up 65 vs 70, down_proj 43 vs 64, o_proj 26 vs 33, corrected), so it takes over from 9.
   bool use_gemm = g.kernel == GLOWQ_KERNEL_GEMM;
   if (g.kernel == GLOWQ_KERNEL_AUTO) use_gemm = g.M > kGemvAutoMaxM;
   if (use_gemm && gemm_supported(g)) {

@@ -506,10 +506,13 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   // Without, the first round of tiles goes to the main CTAs only and the rest is dealt over ALL CTAs, so that the
   // CTAs that computed r pick up row tiles afterwards instead of idling through a long launch.
   const bool deal_all = (p.SK == 1 && p.n_r_ctas > 0);
+  // The leftover tiles are dealt in the order [R CTAs, main CTAs]: an R CTA is free again about two microseconds
+  // into the launch, a main CTA only after its first tile.
   auto tile_at = [&](int k) -> int {
     if (!deal_all) return first_tile + k * tile_step;
-    if (r_only) return n_main + static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x);
-    return k == 0 ? static_cast<int>(blockIdx.x) : n_main + static_cast<int>(blockIdx.x) + (k - 1) * static_cast<int>(gridDim.x);
+    if (r_only) return n_main + (static_cast<int>(blockIdx.x) - n_main) + k * static_cast<int>(gridDim.x);
+    return k == 0 ? static_cast<int>(blockIdx.x)
+                  : n_main + p.n_r_ctas + static_cast<int>(blockIdx.x) + (k - 1) * static_cast<int>(gridDim.x);
   };
   const int g0 = slice * p.gps;
   const int ng = min(p.G, g0 + p.gps) - g0;
@@ -792,7 +795,16 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       // The grid is persistent - never larger than what is resident at once - so every unit's owner is running
       // while the other CTAs wait (bounded) for r before their first L epilogue.  R loads go out before the
       // dependency wait; x is staged only afterwards, for the row tiles this CTA picks up later.
-      r_units<NT>(p, static_cast<int>(blockIdx.x) - n_main, p.n_r_ctas, red, fin, dep_wait_pending, s_rstd);
+      // With K slices and more units than R CTAs, an R CTA runs ONE unit and the CTAs of the slices that do not apply
+      // the correction (all but slice 0) run the others before their tiles: every unit is then done one round after x
+      // is ready, instead of several rounds on the few R CTAs while slice 0 waits for r.
+      const bool helped = p.SK > 1 && p.n_r_units > p.n_r_ctas;
+      r_units<NT>(p, static_cast<int>(blockIdx.x) - n_main, helped ? (1 << 30) : p.n_r_ctas, red, fin, dep_wait_pending,
+                  s_rstd);
+    } else if (p.r_mode == 1 && p.n_r_ctas > 0 && p.SK > 1 && slice != 0 && p.n_r_units > p.n_r_ctas) {
+      const int helpers = (n_main / p.SK) * (p.SK - 1);
+      const int idx = (static_cast<int>(blockIdx.x) / p.SK) * (p.SK - 1) + slice - 1;
+      r_units<NT>(p, p.n_r_ctas + idx, helpers, red, fin, dep_wait_pending, s_rstd);
     } else if (p.r_mode == 1 && p.n_r_ctas == 0) {
       // no dedicated CTAs: every CTA takes its share of R units (dealt from the last CTA down) before its tiles
       r_units<NT>(p, static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), red, fin,

@@ -7,7 +7,7 @@ Differences from the reference, all on the host side of the same interface:
 * the kernel choice knobs W4A16_KERNEL_OUT_DTYPE / W4A16_GEMV_M_MAX / W4A16_FORCE_GEMM / W4A16_FORCE_GEMV are
   read once when the module is built (the reference re-reads the environment on every call, linear.py:172-177);
   W4A16_GEMV_M_MAX has no built-in default of 128 here: unset, the library switches kernels where it measured the
-  cross-over (16 tokens);
+  cross-over (8 tokens);
   the dequant-cache / chunk / JIT knobs belong to fallbacks that do not exist here;
 * output and scratch buffers are caller-side torch tensors; the library allocates nothing.
 """
@@ -136,7 +136,7 @@ class CudaW4A16Linear(nn.Module):
     def kernel_choice(self, m: int) -> int:
         """Which kernel a call with ``m`` tokens asks for (linear.py:172-181): a FORCE knob wins; otherwise an
         explicitly set W4A16_GEMV_M_MAX sends ``m <= W4A16_GEMV_M_MAX`` to the weight-streaming kernel and anything
-        larger to the tensor-core kernel; with the knob unset the library's own switch-over (16 tokens) applies."""
+        larger to the tensor-core kernel; with the knob unset the library's own switch-over (8 tokens) applies."""
         if self._force_gemm:
             return K.KERNEL_GEMM
         if self._force_gemv:

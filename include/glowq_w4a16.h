@@ -94,7 +94,7 @@ typedef struct glowq_w4a16_group {
   int32_t group_size;
   int32_t r_mode;
   int32_t out_dtype;      /* GLOWQ_OUT_F16 / GLOWQ_OUT_F32 (W4A16_KERNEL_OUT_DTYPE)           */
-  int32_t kernel;         /* GLOWQ_KERNEL_AUTO: streaming kernel for M <= 16, tensor-core GEMM above         */
+  int32_t kernel;         /* GLOWQ_KERNEL_AUTO: streaming kernel for M <= 8, tensor-core GEMM above          */
   int32_t n_members;
   int32_t split_k;        /* 0 = choose; >0 forces the number of K slices of the GEMV         */
   int32_t reserved;       /* must be 0 (GLOWQ_ERR_BAD_ARGUMENT otherwise)                       */

@@ -73,7 +73,7 @@ def test_one_layer_of_each_config(layer, M):
         assert np.abs(r_buf.float().cpu().numpy() - r_want).max() <= 6e-3, (name, ic, M)
 
 
-@pytest.mark.parametrize("M,kernel", [(16, K.KERNEL_GEMM), (32, K.KERNEL_GEMV)])
+@pytest.mark.parametrize("M,kernel", [(8, K.KERNEL_GEMM), (16, K.KERNEL_GEMV)])
 def test_both_kernels_on_the_ragged_group_counts(layer, M, kernel):
     """The kernel the automatic choice would NOT take at this token count, on the q/k/v group (bias, 28 / 40 groups)
     and on down_proj (148 / 108 / 136 groups)."""
