@@ -45,9 +45,10 @@ def parse_args():
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="with N > 1: the library's peer-store all-reduce inside one CUDA graph per step (default), or "
                          "NCCL all-reduces between per-segment graphs")
-    ap.add_argument("--no-push", action="store_true",
-                    help="with N > 1: keep the peer all-reduce a launch of its own instead of letting the row-split "
-                         "linears store their partial sums to the peers from their own epilogue")
+    ap.add_argument("--push", action="store_true",
+                    help="with N > 1: let the row-split linears store their partial sums to the peers from their own "
+                         "epilogue (group.push + the finishing kernel) instead of the one-launch peer all-reduce; "
+                         "measured slower at 2 GPUs (the per-CTA system-scope fences cost more than the launch saves)")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the extra `sweep` and `e2e_host_entry` measurements")
@@ -304,6 +305,8 @@ class GpuArm:
         """ms per step (CUDA events on the launching stream, max over ranks) and the callable that runs one step."""
         torch, dist, stream = self.torch, self.dist, self.stream
         step_fn, segs = step_and_segs
+        if self.world > 1:
+            dist.barrier()       # the ranks enter their first step together (the in-kernel waits for a peer are bounded)
         with torch.cuda.stream(stream):
             for _ in range(max(3, warmup)):
                 step_fn()
@@ -354,7 +357,7 @@ class GpuArm:
         torch = self.torch
         with torch.cuda.stream(self.stream):
             plan = stack.plan(M, corrected=corrected, fuse_groups=not self.args.unfused, split_k=self.args.split_k,
-                              push=self.peer_ar if (self.world > 1 and not self.args.no_push) else None)
+                              push=self.peer_ar if (self.world > 1 and self.args.push) else None)
         ms, run = self.timed(stack, self.make_step(stack, plan), steps, warmup, not self.args.no_graph)
         stack.check_status(plan)
         return ms, run, plan
@@ -476,7 +479,7 @@ def run_gpu(args, shape):
             "vs_baseline": None, "dtype": "f32 accumulate over fp16 x int4 (tensor-core MMA), fp16 out",
             "data": "synthetic", "config": workload_config(args, shape),
             "plan": {"parallelism": f"tp{world}", "cuda_graph": use_graph,
-                     "collective": ((("peer stores from the row-split launch + finishing kernel" if not args.no_push and M <= 8
+                     "collective": ((("peer stores from the row-split launch + finishing kernel" if args.push and M <= 8
                                       else "peer-store all-reduce kernel") if arm.peer_ar is not None else "nccl")
                                     if world > 1 else None),
                      "launches_per_layer": calls_per_layer},

@@ -29,7 +29,13 @@ namespace glowq {
 namespace {
 
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr uint32_t kMbarSpinLimit = 1u << 14;  // x ~2 us suspended per failed try_wait
+// Polls of one mbarrier wait before the kernel gives up (status 2).  A failed try_wait is suspended for about 3 us in
+// hardware, so this is seconds, not milliseconds: under programmatic dependent launch the copy and aux warps of a
+// launch run ahead and then wait for ring / metadata slots that the consumers only free once the PREVIOUS kernel is
+// complete - and with tensor parallelism that kernel may be an all-reduce waiting for a rank that is tens of
+// milliseconds behind.  The drain loop after a failure uses the short limit below.
+constexpr uint32_t kMbarSpinLimit = 1u << 20;
+constexpr uint32_t kDrainSpinLimit = 1u << 12;
 constexpr uint32_t kSuspendHintNs = 2000;  // a waiting thread sleeps in hardware instead of burning issue slots
 
 // ---------------------------------------------------------------- mbarrier / bulk-copy primitives
@@ -278,7 +284,7 @@ __device__ __forceinline__ bool mbar_wait_u32(uint32_t a, uint32_t parity, const
     }
     if (ok) return true;
     if ((++spins & 15u) == 0 && *cx.abort_flag) return false;
-    if (spins > ((cx.mode & 12) ? (kMbarSpinLimit << 6) : kMbarSpinLimit)) {
+    if (spins > kMbarSpinLimit) {
       *cx.abort_flag = 1;
       atomicExch(cx.status, 2u);
       return false;
@@ -609,7 +615,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       // the CTA does not retire under an in-flight copy.
       for (uint32_t j = (issued > static_cast<uint32_t>(S) ? issued - S : 0); j < issued; ++j) {
         uint32_t spins = 0;
-        while (!mbar_try_wait(full_bar + (j % S), (j / S) & 1) && ++spins < kMbarSpinLimit) {
+        while (!mbar_try_wait(full_bar + (j % S), (j / S) & 1) && ++spins < kDrainSpinLimit) {
         }
       }
     }
