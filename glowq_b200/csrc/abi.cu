@@ -202,9 +202,11 @@ GemvPlan make_plan(int M, int IC, int n_tiles, int rank, int sms, int split_k) {
     if (pl.gps == kChunkGroups) break;  // K cannot be sliced any finer
     // One or two tokens: two CTAs per SM (16 consumer warps) are worth more than long K slices, so keep slicing while
     // only one CTA would fit (the per-group shared-memory footprint - staged x, converted scale pairs - grows with
-    // the slice length).  More tokens stage too much x for that; they take what fits.
+    // the slice length) or while the ring would be shallower than four stages (measured on the Llama-2-13B down_proj:
+    // three slices of 40 groups with four stages beat two slices of 56 groups with three, 16.2 vs 17.6 us).  More
+    // tokens stage too much x for that; they take what fits.
     const bool want_two = split_k <= 0 && Mc <= 2 && sk < 8 && n_tiles * (sk + 1) <= 8 * sms;
-    if (pl.stages > 0 && (pl.ctas_per_sm == 2 || !want_two)) break;
+    if (pl.stages > 0 && ((pl.ctas_per_sm == 2 && pl.stages >= 4) || !want_two)) break;
   }
   if (forced_stages > 0 && pl.stages > 0) pl.stages = std::max(2, std::min(forced_stages, pl.stages));
   pl.smem = plan_smem(pl, Mc, pl.stages);

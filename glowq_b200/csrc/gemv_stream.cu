@@ -181,60 +181,63 @@ __device__ __forceinline__ void norm_stats(const GemvParams& p, float* part, flo
 // Stage x[0:M, g0*128 : (g0+ng)*128) into shared memory in MMA B-fragment order: for token m and group gl,
 // 16-byte chunk (i*4 + t) holds the columns 32t+8i+{0,4,1,5,2,6,3,7} of that group, the ones at odd positions of
 // a packed word (1,5,3,7) multiplied by 1/16 (see the consumer loop), and xsum[gl][m] = sum of the group's x in
-// fp32 (for the zero-point term).  Consumer threads only.
+// fp32 (for the zero-point term).  Every consumer warp stages exactly the groups it consumes itself (gl = warp,
+// warp + 8, ... of the slice; sixteen lanes per group, two groups per pass), so no warp waits for another one
+// between "x is ready" and its first MMA: a __syncwarp() publishes the data.
 __device__ __forceinline__ void stage_x(const GemvParams& p, int g0, int ng, unsigned char* xs, float* xsum, int mpad,
                                         const float* s_rstd) {
-  constexpr int kBatch = 4;  // global loads in flight per thread before any of them is consumed
-  const int per_tok = ng * 16;
-  const int total = p.M * per_tok;
-  for (int base = 0; base < total; base += kConsumerThreads * kBatch) {
-    uint4 v[kBatch];
-    int mm[kBatch], cc[kBatch];
+  constexpr int kBatch = 4;  // global loads in flight per lane before any of them is consumed
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hsel = lane >> 4, s = lane & 15;   // s = 8-column block of the group, in source order
+  const int n_mine = ng > warp ? (ng - warp + kConsumerWarps - 1) / kConsumerWarps : 0;
+  const int passes = (n_mine + 1) >> 1;
+  for (int m = 0; m < p.M; ++m) {
+    for (int p0 = 0; p0 < passes; p0 += kBatch) {
+      uint4 v[kBatch];
+      int glv[kBatch];
 #pragma unroll
-    for (int b = 0; b < kBatch; ++b) {
-      const int idx = base + b * kConsumerThreads + threadIdx.x;
-      const bool valid = idx < total;
-      const int m = valid ? idx / per_tok : 0;
-      const int c = valid ? idx - m * per_tok : -1;
-      mm[b] = m;
-      cc[b] = c;
-      v[b] = make_uint4(0, 0, 0, 0);
-      if (valid) {
-        const int k = (g0 + (c >> 4)) * kGroup + 8 * (c & 15);
-        const __half* src = p.x + static_cast<size_t>(m) * p.x_stride + k;
-        if (p.x_vec_ok && k + 8 <= p.IC) {
-          v[b] = *reinterpret_cast<const uint4*>(src);
-          if (p.norm_w != nullptr) v[b] = norm_x8(p, v[b], m, k, s_rstd[m]);
-        } else {
-          __align__(16) __half tmp[8];
+      for (int b = 0; b < kBatch; ++b) {
+        const int gl = warp + kConsumerWarps * (2 * (p0 + b) + hsel);
+        const bool valid = (p0 + b) < passes && gl < ng;
+        glv[b] = valid ? gl : -1;
+        v[b] = make_uint4(0, 0, 0, 0);
+        if (valid) {
+          const int k = (g0 + gl) * kGroup + 8 * s;
+          const __half* src = p.x + static_cast<size_t>(m) * p.x_stride + k;
+          if (p.x_vec_ok && k + 8 <= p.IC) {
+            v[b] = *reinterpret_cast<const uint4*>(src);
+            if (p.norm_w != nullptr) v[b] = norm_x8(p, v[b], m, k, s_rstd[m]);
+          } else {
+            __align__(16) __half tmp[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) tmp[e] = (k + e < p.IC) ? src[e] : __float2half(0.f);
-          v[b] = *reinterpret_cast<const uint4*>(tmp);
+            for (int e = 0; e < 8; ++e) tmp[e] = (k + e < p.IC) ? src[e] : __float2half(0.f);
+            v[b] = *reinterpret_cast<const uint4*>(tmp);
+          }
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) {
+        const __half2* h2 = reinterpret_cast<const __half2*>(&v[b]);
+        float part = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __half22float2(h2[e]);
+          part += f.x + f.y;
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);  // the 16 lanes of one (m, gl)
+        if (glv[b] >= 0) {
+          uint4 o4 = interleave_pairs(v[b]);
+          o4.y = hmul2(o4.y, 0x2C002C00u);
+          o4.w = hmul2(o4.w, 0x2C002C00u);
+          const int i = s & 3, t = s >> 2;
+          *reinterpret_cast<uint4*>(xs + static_cast<size_t>(m) * p.xs_stride + (glv[b] * 16 + i * 4 + t) * 16) = o4;
+          if (s == 0) xsum[glv[b] * mpad + m] = part;
         }
       }
     }
-#pragma unroll
-    for (int b = 0; b < kBatch; ++b) {
-      const __half2* h2 = reinterpret_cast<const __half2*>(&v[b]);
-      float part = 0.f;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f = __half22float2(h2[e]);
-        part += f.x + f.y;
-      }
-#pragma unroll
-      for (int o = 8; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);  // the 16 lanes of one (m, gl)
-      if (cc[b] >= 0) {
-        const int gl = cc[b] >> 4, s = cc[b] & 15;  // s = 8-column block of the group, in source order
-        uint4 o4 = interleave_pairs(v[b]);
-        o4.y = hmul2(o4.y, 0x2C002C00u);
-        o4.w = hmul2(o4.w, 0x2C002C00u);
-        const int i = s & 3, t = s >> 2;
-        *reinterpret_cast<uint4*>(xs + static_cast<size_t>(mm[b]) * p.xs_stride + (gl * 16 + i * 4 + t) * 16) = o4;
-        if (s == 0) xsum[gl * mpad + mm[b]] = part;
-      }
-    }
   }
+  __syncwarp();
 }
 
 // ---------------------------------------------------------------- shared-space (32-bit address) accessors
@@ -487,14 +490,14 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   uint64_t* meta_full = empty_bar + kMaxStages;       // [kMetaDepth]: a tile's raw scales / zero words have landed
   uint64_t* cooked_full = meta_full + kMetaDepth;     // [kCookedDepth]: a tile's converted pairs are written
   uint64_t* cooked_empty = cooked_full + kCookedDepth;  // ... and the consumer warps are done with them
-  uint64_t* red_empty = cooked_empty + kCookedDepth;  // [2]: the aux warp has drained a reduction buffer
+  uint64_t* red_empty = cooked_empty + kCookedDepth;  // the aux warp has drained the reduction buffer
   unsigned char* ring = smem + 256;
   const int meta_bytes = kTileRows * (p.meta_gp * 2 + p.meta_gw * 4);
   unsigned char* meta = ring + static_cast<size_t>(p.stages) * kStageBytes;
   const int cooked_bytes = p.gps * (kTileRows * 8);   // [group][row] float2 {scale * 2^24, -scale * zero}
   unsigned char* cooked = meta + static_cast<size_t>(kMetaDepth) * meta_bytes;
   float* red = reinterpret_cast<float*>(cooked + static_cast<size_t>(kCookedDepth) * cooked_bytes);
-  float* fin = red + 2 * kConsumerWarps * NB * 128;  // red is double-buffered; fin serves the R units only
+  float* fin = red + kConsumerWarps * NB * 128;      // one reduction buffer; fin serves the R units only
   float* xsum = fin + NT * 128;                      // [groups of the slice][8 NT]
   unsigned char* xs = reinterpret_cast<unsigned char*>(xsum + p.gps * (8 * NT));
   unsigned char* zero_row = xs + static_cast<size_t>(p.M) * p.xs_stride;
@@ -540,10 +543,10 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       mbar_init(cooked_full + i, 1);
       mbar_init(cooked_empty + i, kConsumerWarps);
     }
-    mbar_init(red_empty + 0, 1);
-    mbar_init(red_empty + 1, 1);
+    mbar_init(red_empty, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (threadIdx.x >= 32 && threadIdx.x < 32 + kZeroRowBytes / 4) reinterpret_cast<uint32_t*>(zero_row)[threadIdx.x - 32] = 0u;
   __syncthreads();
   if (threadIdx.x == 0) trace_event(p, 1);
   Ctx cx{&s_abort, p.ws_head + WS_STATUS, tuning_bits(p)};
@@ -560,11 +563,10 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     bool ok = true;
     for (int k = 0, tile; (tile = tile_at(k)) < p.n_tiles && ok; ++k) {
       const TileInfo ti = tile_info(p, tile, slice);
-      // one row tile ahead of the ring, the same chunk goes to L2: while the ring is full (launch prologue, epilogues)
-      // HBM keeps streaming, and the ring's own copies then hit L2
-      const int tile_next = tile_at(k + 1);
-      const bool have_next = p.deep_prefetch && tile_next < p.n_tiles;
-      const TileInfo ti_next = tile_info(p, have_next ? tile_next : tile, slice);
+      // L2 lookahead: with every weight chunk handed to the ring, the chunk that will follow S issues later (a later
+      // chunk of this tile or one of the CTA's next tiles) is requested from L2.  The ring is only S stages deep, so
+      // at the start of a launch - all slots filled, consumers still waiting for x - the chunks beyond it would
+      // otherwise be fetched from HBM one by one as slots free up, each exposing a full DRAM round trip.
       for (int c = 0; c < n_chunks; ++c) {
         if (!(ok = mbar_wait_u32(empty_u32 + st * 8, ph ^ 1, cx))) break;
         if (lane == 0) {
@@ -574,7 +576,15 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
             mbar_arrive_expect_tx(full_bar + st, kStageBytes);
             tma_load_2d(ring + static_cast<size_t>(st) * kStageBytes, &tm.w[ti.mi], (g0 + c * kChunkGroups) * 16, ti.row0,
                         full_bar + st);
-            if (have_next) tma_prefetch_2d(&tm.w[ti_next.mi], (g0 + c * kChunkGroups) * 16, ti_next.row0);
+            if (p.deep_prefetch) {
+              const int pi = k * n_chunks + c + S;              // weight chunk index (within this CTA) S issues ahead
+              const int kp = pi / n_chunks, cp = pi - kp * n_chunks;
+              const int tile_p = tile_at(kp);
+              if (tile_p < p.n_tiles) {
+                const TileInfo tp_ = tile_info(p, tile_p, slice);
+                tma_prefetch_2d(&tm.w[tp_.mi], (g0 + cp * kChunkGroups) * 16, tp_.row0);
+              }
+            }
           }
         }
         ++issued;
@@ -702,7 +712,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
         asm volatile("bar.sync 2, %0;" ::"n"(kConsumerThreads + 32) : "memory");
       else
         asm volatile("bar.sync 3, %0;" ::"n"(kConsumerThreads + 32) : "memory");
-      const float4* red4 = reinterpret_cast<const float4*>(red) + static_cast<size_t>(buf) * kConsumerWarps * NB * 32;
+      const float4* red4 = reinterpret_cast<const float4*>(red);
       float4 v[NB];
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
@@ -717,8 +727,8 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(red_empty + buf);  // the consumers may refill this buffer
-      buf ^= 1;
+      if (lane == 0) mbar_arrive(red_empty);  // the consumers may refill the buffer
+      buf ^= 1;                               // (the named barriers alternate)
       bool finalize = true;
       if (p.SK > 1) {
         // every K slice parks its tile; the last slice to arrive adds them up in slice order (deterministic)
@@ -819,9 +829,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     if (threadIdx.x == 0 && r_only) trace_event(p, 6);
     if (dep_wait_pending) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x == 0) trace_event(p, 2);
-    if (!r_only || deal_all) stage_x(p, g0, ng, xs, xsum, 8 * NT, s_rstd);
-    if (threadIdx.x < kZeroRowBytes / 4) reinterpret_cast<uint32_t*>(zero_row)[threadIdx.x] = 0u;
-    consumer_sync();  // publishes xs / xsum / the zero row
+    if (!r_only || deal_all) stage_x(p, g0, ng, xs, xsum, 8 * NT, s_rstd);   // per warp: no CTA-wide barrier needed
     if (threadIdx.x == 0) trace_event(p, 3);
 
     // per-lane constant shared addresses: weight quad (warp's group, lane's 16 B, lane's row), x chunk, x sums, the
@@ -988,9 +996,9 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       if (lane == 0) mbar_arrive_u32(cempty_u32 + cslot * 8);   // the aux warp may convert the tile after next into this slot
 
       // park the partial sums
-      ok = ok && mbar_wait_u32(rempty_u32 + rbuf * 8, rph ^ 1, cx);
+      ok = ok && mbar_wait_u32(rempty_u32, rph ^ 1, cx);   // the aux warp has drained the previous tile's sums
       {
-        float4* red4 = reinterpret_cast<float4*>(red) + static_cast<size_t>(rbuf) * kConsumerWarps * NB * 32;
+        float4* red4 = reinterpret_cast<float4*>(red);
 #pragma unroll
         for (int b = 0; b < NB; ++b)
           red4[(warp * NB + b) * 32 + lane] = make_float4(acc[b][0], acc[b][1], acc[b][2], acc[b][3]);
@@ -1000,7 +1008,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
         // eight partial sums themselves - one output element each per fragment block - instead of handing the
         // tile to the single aux warp.
         consumer_sync();
-        const float* redb = red + static_cast<size_t>(rbuf) * kConsumerWarps * NB * 128;
+        const float* redb = red;
         for (int e = threadIdx.x; e < NB * 128; e += kConsumerThreads) {
           const int b = e >> 7, ln = (e & 127) >> 2, cc = e & 3;
           const int j = b / NT, nt = b - j * NT;
@@ -1028,7 +1036,8 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
         asm volatile("bar.arrive 2, %0;" ::"n"(kConsumerThreads + 32) : "memory");
       else
         asm volatile("bar.arrive 3, %0;" ::"n"(kConsumerThreads + 32) : "memory");
-      if ((rbuf ^= 1) == 0) rph ^= 1;
+      rbuf ^= 1;
+      rph ^= 1;
       if (threadIdx.x == 0 && k == 0) trace_event(p, 8);
     }
 

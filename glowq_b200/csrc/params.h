@@ -17,7 +17,7 @@ constexpr int kGroup = 128;         // quantisation group of the fast paths
 constexpr int kChunkGroups = 8;     // groups per pipeline stage: 1024 input columns = 512 packed bytes per row
 constexpr int kRowPitch = kChunkGroups * 64;  // stage row pitch in shared memory: the dense box a 2-D TMA copy writes
 constexpr int kStageBytes = kTileRows * kRowPitch;
-constexpr int kMetaDepth = 3;       // tiles of scale / zero-point metadata in flight
+constexpr int kMetaDepth = 2;       // tiles of raw scale / zero-point metadata in flight
 constexpr int kMaxStages = 8;
 constexpr unsigned kSpinLimit = 1u << 18;  // bound of every device-side wait loop
 
@@ -32,7 +32,7 @@ inline size_t gemv_smem_layout_bytes(int stages, int meta_gp, int meta_gw, int g
   off += static_cast<size_t>(stages) * kStageBytes;
   off += static_cast<size_t>(kMetaDepth) * kTileRows * (meta_gp * 2 + meta_gw * 4);
   off += static_cast<size_t>(kCookedDepth) * gps * (kTileRows * 8);
-  off += static_cast<size_t>(2 * kConsumerWarps) * kRowTiles * NT * 512 + static_cast<size_t>(NT) * 512;
+  off += static_cast<size_t>(kConsumerWarps) * kRowTiles * NT * 512 + static_cast<size_t>(NT) * 512;
   off += static_cast<size_t>(gps) * NT * 32;
   off += static_cast<size_t>(M) * xs_stride;
   off += kZeroRowBytes;
