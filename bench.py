@@ -45,10 +45,11 @@ def parse_args():
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="with N > 1: the library's peer-store all-reduce inside one CUDA graph per step (default), or "
                          "NCCL all-reduces between per-segment graphs")
-    ap.add_argument("--push", action="store_true",
+    ap.add_argument("--push", default="auto", choices=["auto", "on", "off"],
                     help="with N > 1: let the row-split linears store their partial sums to the peers from their own "
-                         "epilogue (group.push + the finishing kernel) instead of the one-launch peer all-reduce; "
-                         "measured slower at 2 GPUs (the per-CTA system-scope fences cost more than the launch saves)")
+                         "epilogue (group.push + the finishing kernel) instead of the one-launch peer all-reduce. "
+                         "auto: for one or two tokens, where it measured ahead (8-byte words per element cost more "
+                         "than they save from a handful of tokens on)")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the extra `sweep` and `e2e_host_entry` measurements")
@@ -352,12 +353,18 @@ class GpuArm:
                 ms = float(t.item())
         return ms / steps, run
 
+    def pushes(self, M):
+        """Whether the row-split launches of an M-token step store to the peers themselves."""
+        if self.world == 1 or self.peer_ar is None or self.args.push == "off":
+            return False
+        return M <= (2 if self.args.push == "auto" else 8)
+
     def decode(self, stack, M, steps, warmup, corrected=True):
         """Time one decode configuration; returns (ms per step, run callable, plan)."""
         torch = self.torch
         with torch.cuda.stream(self.stream):
             plan = stack.plan(M, corrected=corrected, fuse_groups=not self.args.unfused, split_k=self.args.split_k,
-                              push=self.peer_ar if (self.world > 1 and self.args.push) else None)
+                              push=self.peer_ar if self.pushes(M) else None)
         ms, run = self.timed(stack, self.make_step(stack, plan), steps, warmup, not self.args.no_graph)
         stack.check_status(plan)
         return ms, run, plan
@@ -479,7 +486,7 @@ def run_gpu(args, shape):
             "vs_baseline": None, "dtype": "f32 accumulate over fp16 x int4 (tensor-core MMA), fp16 out",
             "data": "synthetic", "config": workload_config(args, shape),
             "plan": {"parallelism": f"tp{world}", "cuda_graph": use_graph,
-                     "collective": ((("peer stores from the row-split launch + finishing kernel" if args.push and M <= 8
+                     "collective": ((("peer stores from the row-split launch + finishing kernel" if arm.pushes(M)
                                       else "peer-store all-reduce kernel") if arm.peer_ar is not None else "nccl")
                                     if world > 1 else None),
                      "launches_per_layer": calls_per_layer},

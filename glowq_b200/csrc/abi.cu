@@ -275,7 +275,7 @@ int validate_group(const glowq_w4a16_group_t& g) {
     if (pp.world < 1 || pp.world > GLOWQ_MAX_RANKS || pp.rank < 0 || pp.rank >= pp.world || !pp.epoch)
       return GLOWQ_ERR_BAD_ARGUMENT;
     for (int r = 0; r < pp.world; ++r)
-      if (!pp.buf[r] || !pp.flag[r]) return GLOWQ_ERR_BAD_ARGUMENT;
+      if (!pp.ll_buf[r]) return GLOWQ_ERR_BAD_ARGUMENT;
     const long long n = static_cast<long long>(g.M) * g.members[0].OC;
     if (g.n_members != 1 || g.out_dtype != GLOWQ_OUT_F16 || g.members[0].out_stride != g.members[0].OC ||
         g.M > kGemvMaxM || n > pp.max_n || (n & 7) || g.push_site < 0 || g.push_site >= pp.sites ||
@@ -388,10 +388,7 @@ int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cuda
       const glowq_w4a16_peers_t& pp = *g.push;
       p.push_world = pp.world;
       const size_t slot = (static_cast<size_t>(g.push_site) * pp.world + pp.rank) * pp.max_n;
-      for (int r = 0; r < pp.world; ++r) {
-        p.push_slot[r] = static_cast<__half*>(pp.buf[r]) + slot;
-        p.push_flag[r] = static_cast<uint32_t*>(pp.flag[r]) + g.push_site * pp.world + pp.rank;
-      }
+      for (int r = 0; r < pp.world; ++r) p.push_slot[r] = static_cast<uint2*>(pp.ll_buf[r]) + slot;
       p.push_epoch = static_cast<uint32_t*>(pp.epoch) + g.push_site;
     }
 

@@ -1,23 +1,31 @@
 // Weight-streaming corrected W4A16 kernel for small token counts (decode).  One launch computes, for every
 // member i of a group,   y_i = x . dequant(Q_i)^T + alpha_i * (x . R^T) . L_i^T + bias_i.
 //
-// Persistent CTAs (one or two per SM), each with ten warps:
+// Persistent CTAs (two per SM where shared memory allows), each with ten warps:
 //   * warp 8 streams packed weights: for every 32-row tile of the CTA it issues one 2-D TMA copy per pipeline
 //     stage (32 rows x 8 quantisation groups = 16 KB) into a shared-memory ring guarded by mbarriers, and after
-//     a tile's weight stages the tile's rows of L_i.  It depends on no other warp's results, so HBM stays busy
-//     across tile boundaries, reductions and epilogues.
-//   * warp 9 fetches the tile's scales and zero-point words a few tiles ahead into a small metadata ring.
+//     a tile's weight stages the tile's rows of L_i.  It depends on no other warp's results.  The ring is shallow,
+//     so it also asks L2 for the chunk that follows a few issues later, and - once all of its own copies are issued -
+//     for its share of the head of the NEXT call's weights (a hint the caller may give).
+//   * warp 9 fetches each tile's raw scales and zero-point words two tiles ahead (4-byte cp.async), converts them one
+//     tile ahead of the consumers into fp32 pairs {scale * 2^24, -scale * zero} laid out [group][row], and finishes
+//     tiles: it adds the consumer warps' partial sums in warp order, runs the split-K combine, adds the bias and
+//     stores.  Only a CTA's last tile is summed by the consumer threads themselves.
 //   * warps 0-7 consume: warp w owns group w of every stage.  Lane (g = lane/4, t = lane%4) reads rows g, g+8,
 //     g+16, g+24 with one 128-bit shared load each - the four lanes of a quad cover the 64 B of one group - masks
 //     the codes into fp16 subnormals (no conversion arithmetic) and feeds m16n8k16 tensor-core MMAs against the
-//     activations staged once per CTA in B-fragment order (tokens on the MMA N axis, so up to 8 tokens cost what
-//     one token costs).  Each group's fp32 result is scaled by its fp16 scale, and the zero-point is applied as
-//     -z * scale * sum(x over the group), in fp32.
-//   * r = R_g . x is produced inside the launch by "R units" (16 rows of R x a K slice) run by a few extra CTAs at
-//     the end of the grid; each unit stores an fp32 slot and bumps a release counter, and whoever needs r adds the
-//     slots of an R tile in slot order (identical bits everywhere) and rounds to fp16.  The grid never exceeds what
-//     is resident at once, so the bounded wait before the first L_i epilogue never depends on an unscheduled CTA.
+//     activations it staged itself in B-fragment order (tokens on the MMA N axis, so up to 8 tokens stream the
+//     weights once).  Each group's fp32 result takes two FMAs with the converted pair: the scale, and the zero-point
+//     as -z * scale * sum(x over the group).
+//   * Optionally the activations are transformed while they are staged: residual add and RMSNorm.
+//   * r = R_g . x is produced inside the launch by "R units" (16 rows of R x a K slice) run by extra CTAs at the end
+//     of the grid (and, with K slices, by the CTAs of slices that apply no correction); each unit stores an fp32 slot,
+//     a CTA publishes its units with one add to a release counter, and whoever needs r adds the slots of an R tile in
+//     slot order (identical bits everywhere) and rounds to fp16.  The grid never exceeds what is resident at once, so
+//     the bounded wait before the first L_i epilogue never depends on an unscheduled CTA.
 //   * K can be sliced across CTAs; the last CTA to arrive at a tile sums the slices in slice order.
+//   * Tensor-parallel row-split launches may store their result to every rank's staging slot themselves, as 8-byte
+//     words {fp16 value, call epoch}; a small finishing kernel polls the words and adds them in rank order.
 // Every wait (mbarrier, release counter) is bounded; on expiry the kernel records a status word and drains.
 #include <cstdlib>
 
@@ -504,6 +512,10 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int S = p.stages;
+  // Epoch stamped into the pushed words: this site's call counter + 1.  The counter only moves when the last CTA of a
+  // pushing launch leaves; it is read AFTER the wait for the previous kernels (a launch may start long before its
+  // predecessors are complete), by the roles that store outputs.
+  uint32_t push_e = 0u;
   // The last n_r_ctas CTAs of the grid only compute r (their copy / aux warps have no tiles): a CTA that ran an R
   // unit AND a full share of row tiles would finish microseconds after the others and set the kernel's length.
   const int n_main = static_cast<int>(gridDim.x) - p.n_r_ctas;
@@ -705,7 +717,10 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       if (last && p.SK == 1) break;   // the consumer warps finish this tile themselves
 
       // ---- epilogue of `tile` (outputs may still be read by the previous kernel until it has completed)
-      if (k == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+      if (k == 0) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (p.push_world > 0) push_e = *p.push_epoch + 1u;
+      }
       const TileInfo ti = tile_info(p, tile, slice);
       const MemberDev& mb = p.mem[ti.mi];
       if (buf == 0)
@@ -778,7 +793,8 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
               } else {
                 const __half h = __float2half_rn(o);
                 static_cast<__half*>(mb.out)[idx] = h;
-                for (int r = 0; r < p.push_world; ++r) p.push_slot[r][idx] = h;   // plain peer stores (out_stride == OC)
+                // one 8-byte peer store per rank: {value, epoch} (out_stride == OC, so idx is the dense index)
+                for (int r = 0; r < p.push_world; ++r) p.push_slot[r][idx] = make_uint2(__half_as_ushort(h), push_e);
               }
             }
           }
@@ -828,6 +844,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     }
     if (threadIdx.x == 0 && r_only) trace_event(p, 6);
     if (dep_wait_pending) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (p.push_world > 0) push_e = *p.push_epoch + 1u;
     if (threadIdx.x == 0) trace_event(p, 2);
     if (!r_only || deal_all) stage_x(p, g0, ng, xs, xsum, 8 * NT, s_rstd);   // per warp: no CTA-wide barrier needed
     if (threadIdx.x == 0) trace_event(p, 3);
@@ -1025,7 +1042,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
             } else {
               const __half h = __float2half_rn(o);
               static_cast<__half*>(mb.out)[idx] = h;
-              for (int r = 0; r < p.push_world; ++r) p.push_slot[r][idx] = h;
+              for (int r = 0; r < p.push_world; ++r) p.push_slot[r][idx] = make_uint2(__half_as_ushort(h), push_e);
             }
           }
         }
@@ -1056,21 +1073,14 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   __syncthreads();
   if (threadIdx.x == 0) trace_event(p, 10);
   if ((p.r_mode == 1 || p.push_world > 0) && threadIdx.x == 0) {
-    if (p.push_world > 0) __threadfence_system();   // this CTA's peer stores are ordered before the flags below
     const uint32_t old = atomicAdd(p.ws_head + WS_EXIT, 1u);
     if (old == gridDim.x - 1) {  // last CTA out re-arms the counters for the next launch
       p.ws_head[WS_R_DONE] = 0u;
       p.ws_head[WS_EXIT] = 0u;
+      // every CTA has read the site's call counter by now (each one stamped its stores with counter + 1): advance it
+      // for the finishing kernel, which runs after this launch on the same stream
+      if (p.push_world > 0) *p.push_epoch = push_e;
       __threadfence();
-      if (p.push_world > 0) {
-        // every CTA's stores are out: publish this call's epoch on every rank (the finishing kernel of each rank waits
-        // for all sources' flags of the site to reach its own epoch)
-        const uint32_t e = *p.push_epoch + 1u;
-        *p.push_epoch = e;
-        __threadfence_system();
-        for (int r = 0; r < p.push_world; ++r)
-          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.push_flag[r]), "r"(e) : "memory");
-      }
     }
   }
 }

@@ -85,24 +85,22 @@ struct GemvParams {
   int debug;                     // tuning experiments only (0 in production)
   int l_cols;                    // columns of L per pipeline stage: min(rank, 256)
   int meta_gp, meta_gw;          // per-row metadata pitch: scale halves, zero words (of one K slice)
-  int deep_prefetch;             // the copy warp also asks L2 for the same chunk of its NEXT row tile
+  int deep_prefetch;             // the copy warp also asks L2 for the chunk that follows S issues later
   // Byte ranges of the group call that follows on the stream (a prefix of its packed rows in tile order, its right
   // factor): every CTA's copy warp asks L2 for its share once its own copies are issued, so that HBM keeps streaming
   // through this launch's tail and the next launch's prologue.
   int n_pf;
   const unsigned char* pf_ptr[kMaxPrefetch];
   unsigned pf_bytes[kMaxPrefetch];
-  // Tensor-parallel push (row-split linears): push_slot[r] = rank r's staging slot for THIS rank's partial result
-  // ([M][OC] fp16, dense), push_flag[r] = the epoch flag this rank releases on rank r, push_epoch = local call counter
-  // of the site.  push_world == 0: no push.
   // fused residual add + RMSNorm of the activations (norm_w == nullptr: none)
   const __half* norm_w;
   const __half* residual;
   __half* hidden_out;
   float norm_eps;
+  // Tensor-parallel push (row-split linears): push_slot[r] = rank r's staging slot for THIS rank's partial result
+  // ([M][OC] 8-byte words {fp16 value, epoch}), push_epoch = local call counter of the site.  push_world == 0: none.
   int push_world;
-  __half* push_slot[kMaxRanks];
-  uint32_t* push_flag[kMaxRanks];
+  uint2* push_slot[kMaxRanks];
   uint32_t* push_epoch;
   MemberDev mem[kMaxMembers];
 };

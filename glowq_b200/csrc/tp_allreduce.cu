@@ -31,6 +31,7 @@ unsigned ar_spin_limit() {
 }
 
 struct ArParams {
+  const uint2* ll_local;                 // finish only: this rank's word buffer [sites][world][max_n] {value, epoch}
   unsigned char* buf[GLOWQ_MAX_RANKS];   // staging buffer of every rank: [sites][world][max_n] fp16
   uint32_t* flag[GLOWQ_MAX_RANKS];       // epoch flags of every rank: [sites][world]
   uint32_t* epoch;                       // local: [sites] calls made so far per site
@@ -66,6 +67,31 @@ __global__ void __launch_bounds__(kArThreads) allreduce_push_kernel(const __grid
       uint32_t* f = p.flag[threadIdx.x] + p.site * p.world + p.rank;
       asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(e) : "memory");
     }
+  }
+  if (p.finish_only) {
+    // The producing launches stored every element as one 8-byte word {fp16 value, epoch}: poll each word until it
+    // carries this call's epoch (bounded), add the ranks' values in rank order.
+    const uint2* mine = p.ll_local + static_cast<size_t>(p.site) * p.world * p.max_n;
+    __half* dst = p.inout;
+    for (int i = threadIdx.x; i < p.n; i += kArThreads) {
+      float acc = 0.f;
+      for (int r = 0; r < p.world; ++r) {
+        const uint2* w = mine + static_cast<size_t>(r) * p.max_n + i;
+        uint2 v;
+        unsigned spins = 0;
+        for (;;) {
+          asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(w) : "memory");
+          if (v.y == e) break;
+          if (++spins > p.spin_limit) {
+            atomicExch(p.status, 4u);
+            break;
+          }
+        }
+        acc += __half2float(__ushort_as_half(static_cast<unsigned short>(v.x)));
+      }
+      dst[i] = __float2half_rn(acc);
+    }
+    return;
   }
   if (threadIdx.x < p.world) {
     const uint32_t* f = p.flag[p.rank] + p.site * p.world + threadIdx.x;
@@ -117,6 +143,10 @@ int launch_allreduce(const glowq_w4a16_peers_t* peers, void* inout, int n, int s
   if ((n & 7) || (reinterpret_cast<uintptr_t>(inout) & 15) || n > peers->max_n || site >= peers->sites)
     return GLOWQ_ERR_UNSUPPORTED_SHAPE;
   ArParams p{};
+  if (finish_only) {
+    if (!peers->ll_buf[peers->rank]) return GLOWQ_ERR_BAD_ARGUMENT;
+    p.ll_local = static_cast<const uint2*>(peers->ll_buf[peers->rank]);
+  }
   for (int r = 0; r < peers->world; ++r) {
     if (!peers->buf[r] || !peers->flag[r]) return GLOWQ_ERR_BAD_ARGUMENT;
     p.buf[r] = static_cast<unsigned char*>(peers->buf[r]);

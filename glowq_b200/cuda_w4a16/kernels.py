@@ -52,7 +52,7 @@ MAX_RANKS = 8
 class Peers(ctypes.Structure):
     _fields_ = [("buf", ctypes.c_void_p * MAX_RANKS), ("flag", ctypes.c_void_p * MAX_RANKS), ("epoch", ctypes.c_void_p),
                 ("status", ctypes.c_void_p), ("world", ctypes.c_int32), ("rank", ctypes.c_int32),
-                ("sites", ctypes.c_int32), ("max_n", ctypes.c_int32)]
+                ("sites", ctypes.c_int32), ("max_n", ctypes.c_int32), ("ll_buf", ctypes.c_void_p * MAX_RANKS)]
 
 
 EXPORTS = ("glowq_w4a16_version", "glowq_w4a16_strerror", "glowq_w4a16_last_cuda_error", "glowq_w4a16_dequant",

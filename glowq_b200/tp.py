@@ -106,8 +106,9 @@ class PeerAllReduce:
             raise ValueError(f"at most {K.MAX_RANKS} ranks")
         self.max_n = (int(max_elems) + 7) // 8 * 8
         flag_bytes = 256 * ((self.SITES * self.world * 4 + 255) // 256)
-        buf_bytes = self.SITES * self.world * self.max_n * 2
-        self.mem = symm.empty(flag_bytes + buf_bytes, dtype=torch.uint8, device=device)
+        buf_bytes = 256 * ((self.SITES * self.world * self.max_n * 2 + 255) // 256)
+        ll_bytes = self.SITES * self.world * self.max_n * 8      # {value, epoch} words of launches that push themselves
+        self.mem = symm.empty(flag_bytes + buf_bytes + ll_bytes, dtype=torch.uint8, device=device)
         self.mem.zero_()
         self.handle = symm.rendezvous(self.mem, group)
         self.local = torch.zeros(64, dtype=torch.int32, device=device)   # [0:SITES] epochs, [32] status
@@ -116,6 +117,7 @@ class PeerAllReduce:
         for r in range(self.world):
             self.peers.flag[r] = ptrs[r]
             self.peers.buf[r] = ptrs[r] + flag_bytes
+            self.peers.ll_buf[r] = ptrs[r] + flag_bytes + buf_bytes
         self.peers.epoch = self.local.data_ptr()
         self.peers.status = self.local.data_ptr() + 32 * 4
         self.peers.world, self.peers.rank = self.world, self.rank

@@ -105,10 +105,10 @@ typedef struct glowq_w4a16_group {
    * no counterpart (its launches are independent: csrc/gemv_w4a16.cu:194-211). */
   const struct glowq_w4a16_group* next;
   /* Optional, tensor-parallel row-split linears (o_proj, down_proj shards): besides writing `out`, the launch stores
-   * its result - this rank's partial sum - into slot [push_site][rank] of EVERY rank's staging buffer as its tiles
-   * finish, and releases the per-(site, rank) epoch flags once the whole launch is complete: the first half of
-   * glowq_w4a16_allreduce_f16 without a launch of its own.  glowq_w4a16_allreduce_finish_f16 (same peers, same site)
-   * waits for all ranks' flags and adds the slots.  Requirements: one member, fp16 output, out_stride == OC,
+   * its result - this rank's partial sum - into slot [push_site][rank] of EVERY rank's `ll_buf` as its tiles finish,
+   * each element as one 8-byte word {value, epoch}: the first half of glowq_w4a16_allreduce_f16 without a launch of
+   * its own, without fences and without flags.  glowq_w4a16_allreduce_finish_f16 (same peers, same site) polls the
+   * words of all ranks' slots until they carry the call's epoch and adds them.  Requirements: one member, fp16 output, out_stride == OC,
    * M * OC <= peers->max_n and a multiple of 8, M <= 8 (the weight-streaming kernel); GLOWQ_ERR_UNSUPPORTED_SHAPE
    * otherwise.  NULL = no push.  See glowq_w4a16_peers_t below for the buffers. */
   const struct glowq_w4a16_peers* push;
@@ -214,13 +214,18 @@ typedef struct glowq_w4a16_peers {
   void* epoch;
   void* status;
   int32_t world, rank, sites, max_n;
+  /* Only for launches that push their result themselves (glowq_w4a16_group_t.push): every rank's second staging
+   * buffer of sites * world * max_n 8-byte words, zeroed once and mapped into every rank like `buf`.  A pushed
+   * element travels as ONE 8-byte store {fp16 value, epoch of the call}: the finishing kernel polls each word until
+   * it carries the current epoch, so neither fences nor flags are involved.  NULL entries: push is refused. */
+  void* ll_buf[GLOWQ_MAX_RANKS];
 } glowq_w4a16_peers_t;
 int glowq_w4a16_allreduce_f16(const glowq_w4a16_peers_t* peers, void* inout, int n, int site, void* stream);
 
-/* Second half of the all-reduce for a launch that pushed its result itself (glowq_w4a16_group_t.push): wait - bounded,
- * status 4 on expiry - until every rank's flag of `site` carries the epoch of this rank's latest push on that site,
- * add the `world` slots of the local staging buffer in rank order (fp32) and write the n fp16 sums to `out`.  Every
- * rank calls it after its pushing launch, on the same stream; the sums are bit-identical on all ranks. */
+/* Second half of the all-reduce for a launch that pushed its result itself (glowq_w4a16_group_t.push): poll - bounded,
+ * status 4 on expiry - every element of every rank's slot of `site` in the local `ll_buf` until it carries the epoch
+ * of this rank's latest push on that site, add the `world` values in rank order (fp32) and write the n fp16 sums to
+ * `out`.  Every rank calls it after its pushing launch, on the same stream; the sums are bit-identical on all ranks. */
 int glowq_w4a16_allreduce_finish_f16(const glowq_w4a16_peers_t* peers, void* out, int n, int site, void* stream);
 
 /* Bytes of workspace a group call with these sizes needs (sync words + split-K partial sums). */
