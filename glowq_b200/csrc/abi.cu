@@ -213,9 +213,8 @@ GemvPlan make_plan(int M, int IC, int n_tiles, int rank, int sms, int split_k) {
   pl.n_r_tiles = ceil_div(std::max(rank, 0), kRTileRows);
   pl.SKr = chunks;   // one quantisation group per warp and R unit: a single round of loads per unit
   const size_t tile_elems = static_cast<size_t>(kRowTiles) * pl.NT * 128;
-  size_t off = kWsHeaderBytes;
-  pl.off_r_ctr = off;
-  off += kMaxRTiles * 4;
+  pl.off_r_ctr = kWsHeaderBytes;
+  size_t off = kWsTileCtrOffset;
   pl.off_tile_ctr = off;
   off = align_up(off + static_cast<size_t>(n_tiles) * 4, 256);
   pl.off_r_partial = off;
@@ -325,6 +324,7 @@ int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cuda
     p.ws_head = reinterpret_cast<uint32_t*>(ws);
     p.tile_ctr = reinterpret_cast<uint32_t*>(ws + pl.off_tile_ctr);
     p.r_partial = reinterpret_cast<float*>(ws + pl.off_r_partial);
+    p.r_ll = reinterpret_cast<uint2*>(ws + kWsRllOffset);
     p.sk_partial = reinterpret_cast<float*>(ws + pl.off_sk_partial);
     p.M = Mc;
     p.IC = g.IC;

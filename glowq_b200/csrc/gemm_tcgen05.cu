@@ -994,7 +994,7 @@ inline size_t r_slot_bytes(int M, int IC, int rank) {
 // The slots sit at the END of the workspace, clear of the counters that the weight-streaming kernel keeps (zeroed)
 // at its start: one workspace may serve launches of both kernels in turn.
 inline size_t counters_end(int OC_total, int n_members) {
-  const size_t n = kWsHeaderBytes + kMaxRTiles * 4 + (static_cast<size_t>(cdiv(OC_total, kTileRows)) + n_members) * 4;
+  const size_t n = kWsTileCtrOffset + (static_cast<size_t>(cdiv(OC_total, kTileRows)) + n_members) * 4;
   return (n + 255) & ~static_cast<size_t>(255);
 }
 

@@ -324,12 +324,18 @@ __device__ __forceinline__ void cross_warp_reduce(float (&acc)[NB][4], float* re
   consumer_sync();
 }
 
+// Epoch of this launch on its workspace: the counter that the last CTA of every correcting launch advances, + 1.
+// Only valid after the wait for the previous kernels.
+__device__ __forceinline__ uint32_t launch_epoch(const GemvParams& p) { return ld_volatile_u32(p.ws_head + WS_EPOCH) + 1u; }
+
 // R units u0, u0 + ustride, ... of this CTA.  One unit: rows [16 rt, 16 rt + 16) of R times the columns of K slice
 // ks (gpr groups; warp w takes groups w, w + 8, ...), tokens 0..M-1.  The fp32 result goes to the unit's own slot of
-// r_partial; whoever needs r adds the SKr slots of an R tile in slot order (so every reader, and r_buf, see the same
-// bits).  R is static: the first round's loads and L2 prefetch requests for every later round of the CTA go out
+// r_partial.  R is static: the first round's loads and L2 prefetch requests for every later round of the CTA go out
 // before the wait for the previous kernel, and the CTA publishes all of its units with ONE fence and one add to the
-// release counter - readers need every unit anyway.
+// release counter.  The CTA whose add completes the count adds the SKr slots of every R tile in slot order, rounds
+// to fp16 and writes r twice: plain into r_buf (for later launches that load it) and as 8-byte words {two elements,
+// epoch of this launch} for the row tiles of this launch, which poll the words they need - one L2 round trip, no
+// flag and no fence on the reading side, and every reader sees the same bits.
 template <int NT>
 __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride, float* red, float* fin,
                                         bool& dep_wait_pending, const float* s_rstd) {
@@ -424,42 +430,58 @@ __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride
     asm volatile("griddepcontrol.wait;" ::: "memory");
     dep_wait_pending = false;
   }
-  __threadfence();
+  const uint32_t epoch = launch_epoch(p);   // in flight while the CTA synchronises below
   consumer_sync();
-  if (threadIdx.x == 0) atomicAdd(p.ws_head + WS_R_DONE, static_cast<uint32_t>(n_done));
-}
-
-// Eight consecutive elements r[tok][j .. j+8) (j a multiple of 8) as four half2 registers: the SKr fp32 slots of
-// the R tile added in slot order, then rounded to fp16.
-template <int NT>
-__device__ __forceinline__ uint4 r_frag_from_partials(const GemvParams& p, int tok, int j) {
-  const int rt = j >> 4, nt = tok >> 3;
-  const float* base = p.r_partial + (static_cast<size_t>(rt) * p.SKr * NT + nt) * 128 + (tok & 7) * 16 + (j & 15);
-  float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
-  for (int ks = 0; ks < p.SKr; ++ks) {
-    const float4 q0 = __ldcg(reinterpret_cast<const float4*>(base + static_cast<size_t>(ks) * (NT * 128)));
-    const float4 q1 = __ldcg(reinterpret_cast<const float4*>(base + static_cast<size_t>(ks) * (NT * 128) + 4));
-    lo.x += q0.x; lo.y += q0.y; lo.z += q0.z; lo.w += q0.w;
-    hi.x += q1.x; hi.y += q1.y; hi.z += q1.z; hi.w += q1.w;
+  uint32_t* last_flag = reinterpret_cast<uint32_t*>(fin);   // fin is free again
+  if (threadIdx.x == 0) {
+    // Release / acquire by one thread on behalf of the CTA: the barrier above orders every thread's slot stores
+    // before this thread's fence, and the barrier below orders its second fence before every thread's slot loads.
+    __threadfence();
+    const uint32_t before = atomicAdd(p.ws_head + WS_R_DONE, static_cast<uint32_t>(n_done));
+    const bool last = before + static_cast<uint32_t>(n_done) == static_cast<uint32_t>(p.n_r_units);
+    if (last) __threadfence();
+    *last_flag = last ? 1u : 0u;
   }
-  uint4 out;
-  __half2 h;
-  h = __floats2half2_rn(lo.x, lo.y); out.x = *reinterpret_cast<uint32_t*>(&h);
-  h = __floats2half2_rn(lo.z, lo.w); out.y = *reinterpret_cast<uint32_t*>(&h);
-  h = __floats2half2_rn(hi.x, hi.y); out.z = *reinterpret_cast<uint32_t*>(&h);
-  h = __floats2half2_rn(hi.z, hi.w); out.w = *reinterpret_cast<uint32_t*>(&h);
-  return out;
+  consumer_sync();
+  if (*last_flag != 0u) {
+    const int q4 = p.rank >> 2;  // rank is a multiple of 8
+    for (int i = threadIdx.x; i < p.M * q4; i += kConsumerThreads) {
+      const int tok = i / q4, j = (i - tok * q4) * 4;
+      const float* base = p.r_partial + (static_cast<size_t>(j >> 4) * p.SKr * NT + (tok >> 3)) * 128 + (tok & 7) * 16 + (j & 15);
+      float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int ks0 = 0; ks0 < p.SKr; ks0 += 4) {  // four slots in flight, added in slot order
+        float4 q[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          q[u] = (ks0 + u < p.SKr) ? __ldcg(reinterpret_cast<const float4*>(base + static_cast<size_t>(ks0 + u) * (NT * 128)))
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          s.x += q[u].x; s.y += q[u].y; s.z += q[u].z; s.w += q[u].w;
+        }
+      }
+      const __half2 h01 = __floats2half2_rn(s.x, s.y), h23 = __floats2half2_rn(s.z, s.w);
+      const uint32_t u01 = *reinterpret_cast<const uint32_t*>(&h01), u23 = *reinterpret_cast<const uint32_t*>(&h23);
+      uint2* w = p.r_ll + static_cast<size_t>(tok) * (p.rank >> 1) + (j >> 1);
+      w[0] = make_uint2(u01, epoch);
+      w[1] = make_uint2(u23, epoch);
+      if (p.r_buf != nullptr) *reinterpret_cast<uint2*>(p.r_buf + static_cast<size_t>(tok) * p.rank + j) = make_uint2(u01, u23);
+    }
+  }
 }
 
-// Bounded wait until every R unit of this launch has published its slot.
-__device__ __forceinline__ void wait_r_done(const GemvParams& p, volatile int* abort_flag) {
+// Eight consecutive elements r[tok][j .. j+8) (j a multiple of 8) of THIS launch as four half2 registers: polls the
+// four {two elements, epoch} words until all carry the launch's epoch (bounded).
+__device__ __forceinline__ uint4 r_frag_poll(const GemvParams& p, int tok, int j, uint32_t epoch, volatile int* abort_flag) {
+  const uint2* w = p.r_ll + static_cast<size_t>(tok) * (p.rank >> 1) + (j >> 1);   // 32-byte aligned
   uint32_t spins = 0;
-  while (ld_acquire_u32(p.ws_head + WS_R_DONE) < static_cast<uint32_t>(p.n_r_units)) {
-    __nanosleep(64);
+  for (;;) {
+    const uint4 a = ld_volatile_v4(w), b = ld_volatile_v4(w + 2);
+    if (a.y == epoch && a.w == epoch && b.y == epoch && b.w == epoch) return make_uint4(a.x, a.z, b.x, b.z);
     if (*abort_flag || ++spins > kSpinLimit) {
       *abort_flag = 1;
       atomicExch(p.ws_head + WS_STATUS, 1u);
-      break;
+      return make_uint4(0, 0, 0, 0);
     }
   }
 }
@@ -516,12 +538,20 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   // pushing launch leaves; it is read AFTER the wait for the previous kernels (a launch may start long before its
   // predecessors are complete), by the roles that store outputs.
   uint32_t push_e = 0u;
+  // Epoch of the {elements, epoch} words that carry r of this launch: the workspace's launch counter + 1, read by the
+  // consumer warps after the same wait.
+  uint32_t r_epoch = 0u;
   // The last n_r_ctas CTAs of the grid only compute r (their copy / aux warps have no tiles): a CTA that ran an R
   // unit AND a full share of row tiles would finish microseconds after the others and set the kernel's length.
   const int n_main = static_cast<int>(gridDim.x) - p.n_r_ctas;
-  const bool r_only = static_cast<int>(blockIdx.x) >= n_main;
-  const int slice = blockIdx.x % p.SK;
-  const int first_tile = r_only ? p.n_tiles : static_cast<int>(blockIdx.x) / p.SK;
+  // Logical CTA index: main CTAs 0 .. n_main-1, then the R CTAs.  The R CTAs take the LOWEST block indices, which
+  // the hardware places first: while the previous kernel still holds most CTA slots they are the ones that are
+  // resident early, with their loads of R done before x is ready.
+  const int bid = static_cast<int>(blockIdx.x) >= p.n_r_ctas ? static_cast<int>(blockIdx.x) - p.n_r_ctas
+                                                             : n_main + static_cast<int>(blockIdx.x);
+  const bool r_only = bid >= n_main;
+  const int slice = bid % p.SK;
+  const int first_tile = r_only ? p.n_tiles : bid / p.SK;
   const int tile_step = n_main / p.SK;
   // k-th row tile of this CTA (>= n_tiles: none left).  With K slices every CTA of a slice strides over the tiles.
   // Without, the first round of tiles goes to the main CTAs only and the rest is dealt over ALL CTAs, so that the
@@ -531,9 +561,8 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   // into the launch, a main CTA only after its first tile.
   auto tile_at = [&](int k) -> int {
     if (!deal_all) return first_tile + k * tile_step;
-    if (r_only) return n_main + (static_cast<int>(blockIdx.x) - n_main) + k * static_cast<int>(gridDim.x);
-    return k == 0 ? static_cast<int>(blockIdx.x)
-                  : n_main + p.n_r_ctas + static_cast<int>(blockIdx.x) + (k - 1) * static_cast<int>(gridDim.x);
+    if (r_only) return bid + k * static_cast<int>(gridDim.x);
+    return k == 0 ? bid : n_main + p.n_r_ctas + bid + (k - 1) * static_cast<int>(gridDim.x);
   };
   const int g0 = slice * p.gps;
   const int ng = min(p.G, g0 + p.gps) - g0;
@@ -831,20 +860,21 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       // the correction (all but slice 0) run the others before their tiles: every unit is then done one round after x
       // is ready, instead of several rounds on the few R CTAs while slice 0 waits for r.
       const bool helped = p.SK > 1 && p.n_r_units > p.n_r_ctas;
-      r_units<NT>(p, static_cast<int>(blockIdx.x) - n_main, helped ? (1 << 30) : p.n_r_ctas, red, fin, dep_wait_pending,
+      r_units<NT>(p, bid - n_main, helped ? (1 << 30) : p.n_r_ctas, red, fin, dep_wait_pending,
                   s_rstd);
     } else if (p.r_mode == 1 && p.n_r_ctas > 0 && p.SK > 1 && slice != 0 && p.n_r_units > p.n_r_ctas) {
       const int helpers = (n_main / p.SK) * (p.SK - 1);
-      const int idx = (static_cast<int>(blockIdx.x) / p.SK) * (p.SK - 1) + slice - 1;
+      const int idx = (bid / p.SK) * (p.SK - 1) + slice - 1;
       r_units<NT>(p, p.n_r_ctas + idx, helpers, red, fin, dep_wait_pending, s_rstd);
     } else if (p.r_mode == 1 && p.n_r_ctas == 0) {
       // no dedicated CTAs: every CTA takes its share of R units (dealt from the last CTA down) before its tiles
-      r_units<NT>(p, static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), red, fin,
+      r_units<NT>(p, static_cast<int>(gridDim.x) - 1 - bid, static_cast<int>(gridDim.x), red, fin,
                   dep_wait_pending, s_rstd);
     }
     if (threadIdx.x == 0 && r_only) trace_event(p, 6);
     if (dep_wait_pending) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (p.push_world > 0) push_e = *p.push_epoch + 1u;
+    if (p.r_mode == 1) r_epoch = launch_epoch(p);
     if (threadIdx.x == 0) trace_event(p, 2);
     if (!r_only || deal_all) stage_x(p, g0, ng, xs, xsum, 8 * NT, s_rstd);   // per warp: no CTA-wide barrier needed
     if (threadIdx.x == 0) trace_event(p, 3);
@@ -953,12 +983,6 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
 
       if (threadIdx.x == 0 && k == 0) trace_event(p, 5);
       if (ti.corr) {
-        if (!r_ready) {  // r comes from R units of this launch: bounded wait on the release counter
-          if (lane == 0) wait_r_done(p, &s_abort);
-          __syncwarp();
-          r_ready = true;
-          if (threadIdx.x == 0) trace_event(p, 7);
-        }
         float al[NB][4];
 #pragma unroll
         for (int b = 0; b < NB; ++b) al[b][0] = al[b][1] = al[b][2] = al[b][3] = 0.f;
@@ -978,8 +1002,11 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
 #pragma unroll
               for (int nt = 0; nt < NT; ++nt)
                 rb[nt] = !(kin && tokv[nt]) ? make_uint4(0, 0, 0, 0)
-                         : (p.r_mode == 1)     ? r_frag_from_partials<NT>(p, nt * 8 + g, 256 * l + k)
+                         : (p.r_mode == 1)     ? r_frag_poll(p, nt * 8 + g, 256 * l + k, r_epoch, &s_abort)
                                                : ldg_cg_v4(p.r_buf + static_cast<size_t>(nt * 8 + g) * p.rank + 256 * l + k);
+              __syncwarp();   // lanes may have polled different numbers of times
+              if (threadIdx.x == 0 && !r_ready) trace_event(p, 7);
+              r_ready = true;
               if (l == 0) {
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) rb_keep[nt] = rb[nt];
@@ -1057,17 +1084,6 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       rph ^= 1;
       if (threadIdx.x == 0 && k == 0) trace_event(p, 8);
     }
-
-    // The CTA that ran R unit 0 leaves r in r_buf (fp16) for later launches of the group that load it.
-    if (p.r_mode == 1 && blockIdx.x == gridDim.x - 1) {
-      if (threadIdx.x == 0) wait_r_done(p, &s_abort);
-      consumer_sync();
-      for (int e = threadIdx.x; e < p.M * (p.n_r_tiles * 2); e += kConsumerThreads) {
-        const int tok = e / (p.n_r_tiles * 2), j = (e - tok * (p.n_r_tiles * 2)) * 8;
-        if (j < p.rank)  // rank is a multiple of 8
-          *reinterpret_cast<uint4*>(p.r_buf + static_cast<size_t>(tok) * p.rank + j) = r_frag_from_partials<NT>(p, tok, j);
-      }
-    }
   }
 
   __syncthreads();
@@ -1080,6 +1096,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       // every CTA has read the site's call counter by now (each one stamped its stores with counter + 1): advance it
       // for the finishing kernel, which runs after this launch on the same stream
       if (p.push_world > 0) *p.push_epoch = push_e;
+      if (p.r_mode == 1) p.ws_head[WS_EPOCH] = r_epoch;   // words of this launch never match a later launch's epoch
       __threadfence();
     }
   }

@@ -40,9 +40,15 @@ inline size_t gemv_smem_layout_bytes(int stages, int meta_gp, int meta_gw, int g
 }
 
 // Workspace header (uint32 words); the rest of the workspace follows at kWsHeaderBytes.
-enum : int { WS_TICKET = 0, WS_R_DONE = 1, WS_EXIT = 2, WS_STATUS = 3, WS_HEADER_WORDS = 64 };
+enum : int { WS_TICKET = 0, WS_R_DONE = 1, WS_EXIT = 2, WS_STATUS = 3, WS_EPOCH = 4, WS_HEADER_WORDS = 64 };
 constexpr size_t kWsHeaderBytes = WS_HEADER_WORDS * 4;
 constexpr int kMaxRTiles = 64;      // rank <= 1024
+// After the header: 256 B of per-R-tile words, then r of the running launch as the row tiles read it - 8-byte words
+// {half2(r[tok][2j], r[tok][2j+1]), launch epoch}, up to 8 tokens x rank 1024 - then the tile counters.  Launches of
+// the other kernels keep clear of everything up to the end of the tile counters.
+constexpr size_t kWsRllOffset = kWsHeaderBytes + kMaxRTiles * 4;
+constexpr size_t kWsRllBytes = 8 * 1024 * 4;
+constexpr size_t kWsTileCtrOffset = kWsRllOffset + kWsRllBytes;
 constexpr int kMaxPrefetch = kMaxMembers + 1;
 constexpr int kMaxRanks = 8;        // GLOWQ_MAX_RANKS
 constexpr unsigned kPrefetchSlice = 16u << 10;  // bytes per L2 prefetch request
@@ -72,6 +78,7 @@ struct GemvParams {
   __half* r_buf;
   uint32_t* ws_head;      // header words
   float* r_partial;       // [n_r_tiles][SKr][NT*128] fp32 partial products of r, one slot per R unit
+  uint2* r_ll;            // [M][rank/2] words {two fp16 elements of r, launch epoch}: written by the CTA that completes r
   uint32_t* tile_ctr;     // [n_tiles] arrival counters of the split-K partial sums
   float* sk_partial;      // [n_tiles][SK][kRowTiles*NT*128]
   int M, IC, x_stride, R_stride, G, rank, r_mode, out_fp32, n_members;
