@@ -876,7 +876,9 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     if (p.push_world > 0) push_e = *p.push_epoch + 1u;
     if (p.r_mode == 1) r_epoch = launch_epoch(p);
     if (threadIdx.x == 0) trace_event(p, 2);
-    if (!r_only || deal_all) stage_x(p, g0, ng, xs, xsum, 8 * NT, s_rstd);   // per warp: no CTA-wide barrier needed
+    // per warp: no CTA-wide barrier needed.  A CTA without row tiles (an R CTA of a launch with few tiles) stages
+    // nothing and retires: the kernel is complete when its LAST CTA is.
+    if (tile_at(0) < p.n_tiles) stage_x(p, g0, ng, xs, xsum, 8 * NT, s_rstd);
     if (threadIdx.x == 0) trace_event(p, 3);
 
     // per-lane constant shared addresses: weight quad (warp's group, lane's 16 B, lane's row), x chunk, x sums, the
@@ -988,6 +990,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
         for (int b = 0; b < NB; ++b) al[b][0] = al[b][1] = al[b][2] = al[b][3] = 0.f;
         for (int l = 0; l < n_lstages; ++l) {
           ok = ok && mbar_wait_u32(full_u32 + st * 8, ph, cx);
+          if (threadIdx.x == 0 && k == 0 && l == 0) trace_event(p, 11);
           const int cols = min(256, p.rank - 256 * l);
           const int k = 32 * warp + 8 * t;  // column inside this L stage
           if (ok && 32 * warp < cols) {  // warp-uniform: every lane of the warp takes part in the MMAs below
@@ -1000,10 +1003,15 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
               for (int nt = 0; nt < NT; ++nt) rb[nt] = rb_keep[nt];
             } else {
 #pragma unroll
-              for (int nt = 0; nt < NT; ++nt)
-                rb[nt] = !(kin && tokv[nt]) ? make_uint4(0, 0, 0, 0)
-                         : (p.r_mode == 1)     ? r_frag_poll(p, nt * 8 + g, 256 * l + k, r_epoch, &s_abort)
-                                               : ldg_cg_v4(p.r_buf + static_cast<size_t>(nt * 8 + g) * p.rank + 256 * l + k);
+              for (int nt = 0; nt < NT; ++nt) {
+                if (!(kin && tokv[nt])) {
+                  rb[nt] = make_uint4(0, 0, 0, 0);
+                } else if (p.r_mode != 1) {
+                  rb[nt] = ldg_cg_v4(p.r_buf + static_cast<size_t>(nt * 8 + g) * p.rank + 256 * l + k);
+                } else {
+                  rb[nt] = r_frag_poll(p, nt * 8 + g, 256 * l + k, r_epoch, &s_abort);
+                }
+              }
               __syncwarp();   // lanes may have polled different numbers of times
               if (threadIdx.x == 0 && !r_ready) trace_event(p, 7);
               r_ready = true;
