@@ -399,8 +399,9 @@ int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cuda
       // R units run on dedicated CTAs at the end of the grid (several units each when there are many), so that the
       // r chain (R loads, MMAs, slot, release counter) overlaps the other CTAs' x staging and weight streaming
       static const int max_r_ctas = env_int("GLOWQ_GEMV_R_CTAS", 96);
+      // (the epoch word of the workspace counts the consumer warps of a grid in kEpochShift bits)
+      const int cap = std::min(dev.sms * pl.ctas_per_sm, static_cast<int>(kEpochReaderMask) / kConsumerWarps);
       {
-        const int cap = dev.sms * pl.ctas_per_sm;
         int want = std::min(p.n_r_units, max_r_ctas);
         if (pl.SK > 1) {
           // K slices: the R CTAs take no row tiles afterwards, so give them the CTA slots that do not add a round
@@ -411,7 +412,7 @@ int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cuda
         }
         p.n_r_ctas = std::max(0, std::min(want, cap / 3));
       }
-      int grid = std::min(dev.sms * pl.ctas_per_sm - p.n_r_ctas, n_tiles * pl.SK);
+      int grid = std::min(cap - p.n_r_ctas, n_tiles * pl.SK);
       grid = std::max(pl.SK, grid / pl.SK * pl.SK) + p.n_r_ctas;
       p.l_cols = std::min(std::max(p.rank, 8), 256);
       alignas(64) TensorMaps tm;

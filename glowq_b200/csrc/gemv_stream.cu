@@ -324,9 +324,20 @@ __device__ __forceinline__ void cross_warp_reduce(float (&acc)[NB][4], float* re
   consumer_sync();
 }
 
-// Epoch of this launch on its workspace: the counter that the last CTA of every correcting launch advances, + 1.
-// Only valid after the wait for the previous kernels.
-__device__ __forceinline__ uint32_t launch_epoch(const GemvParams& p) { return ld_volatile_u32(p.ws_head + WS_EPOCH) + 1u; }
+// The wait for the previous kernels of the stream, once per consumer warp.  In a correcting launch lane 0 then
+// registers the warp as a reader of the workspace's epoch word; the value the add returns (kept in lane 0 until the
+// epoch is needed, so that nobody waits for the round trip here) carries the epoch of the PREVIOUS correcting launch.
+__device__ __forceinline__ void dep_wait(const GemvParams& p, bool& pending, uint32_t& eword) {
+  if (!pending) return;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  pending = false;
+  if (p.r_mode == 1 && (threadIdx.x & 31) == 0) eword = atomicAdd(p.ws_head + WS_EPOCH, 1u);
+}
+// Epoch that stamps the words of r in this launch (never 0, the value of a word that was never written).
+__device__ __forceinline__ uint32_t launch_epoch(uint32_t eword) {
+  const uint32_t e = ((__shfl_sync(0xffffffffu, eword, 0) >> kEpochShift) + 1u) & kEpochMask;
+  return e == 0u ? 1u : e;
+}
 
 // R units u0, u0 + ustride, ... of this CTA.  One unit: rows [16 rt, 16 rt + 16) of R times the columns of K slice
 // ks (gpr groups; warp w takes groups w, w + 8, ...), tokens 0..M-1.  The fp32 result goes to the unit's own slot of
@@ -338,7 +349,7 @@ __device__ __forceinline__ uint32_t launch_epoch(const GemvParams& p) { return l
 // flag and no fence on the reading side, and every reader sees the same bits.
 template <int NT>
 __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride, float* red, float* fin,
-                                        bool& dep_wait_pending, const float* s_rstd) {
+                                        bool& dep_wait_pending, uint32_t& eword, const float* s_rstd) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   if (u0 >= p.n_r_units) return;
   uint4 a[4], b[4];
@@ -380,10 +391,7 @@ __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride
     for (int gl = warp; gl < ng || gl == warp; gl += kConsumerWarps) {
       const bool more_rounds = gl + kConsumerWarps < ng;
       if (gl != warp || unit != u0) load_round(unit, gl, true);
-      if (dep_wait_pending) {  // R is static, x is not: the earlier kernels must be complete before x is read
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-        dep_wait_pending = false;
-      }
+      dep_wait(p, dep_wait_pending, eword);  // R is static, x is not: the earlier kernels must be complete before x is read
       if (gl < ng) {
         const int kb = (gbase + gl) * kGroup + 32 * t;
 #pragma unroll
@@ -426,11 +434,7 @@ __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride
     for (int e = threadIdx.x; e < NT * 128; e += kConsumerThreads) slot[e] = fin[e];
     ++n_done;
   }
-  if (dep_wait_pending) {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    dep_wait_pending = false;
-  }
-  const uint32_t epoch = launch_epoch(p);   // in flight while the CTA synchronises below
+  dep_wait(p, dep_wait_pending, eword);
   consumer_sync();
   uint32_t* last_flag = reinterpret_cast<uint32_t*>(fin);   // fin is free again
   if (threadIdx.x == 0) {
@@ -444,6 +448,7 @@ __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride
   }
   consumer_sync();
   if (*last_flag != 0u) {
+    const uint32_t epoch = launch_epoch(eword);
     const int q4 = p.rank >> 2;  // rank is a multiple of 8
     for (int i = threadIdx.x; i < p.M * q4; i += kConsumerThreads) {
       const int tok = i / q4, j = (i - tok * q4) * 4;
@@ -466,6 +471,24 @@ __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride
       w[0] = make_uint2(u01, epoch);
       w[1] = make_uint2(u23, epoch);
       if (p.r_buf != nullptr) *reinterpret_cast<uint2*>(p.r_buf + static_cast<size_t>(tok) * p.rank + j) = make_uint2(u01, u23);
+    }
+    // Nothing of this launch touches the unit counter any more; the epoch moves on once every consumer warp of the
+    // grid has taken it (all CTAs are resident and register right after the wait for the previous kernels, so this
+    // is normally true long before r is complete).  Off the path of r: the words above are already on their way.
+    if (threadIdx.x == 0) {
+      p.ws_head[WS_R_DONE] = 0u;
+      const uint32_t readers = static_cast<uint32_t>(kConsumerWarps) * gridDim.x;
+      uint32_t spins = 0;
+      bool all_in = true;
+      while ((ld_acquire_u32(p.ws_head + WS_EPOCH) & kEpochReaderMask) != readers) {
+        __nanosleep(128);
+        if (++spins > kSpinLimit) {
+          atomicExch(p.ws_head + WS_STATUS, 1u);
+          all_in = false;
+          break;
+        }
+      }
+      if (all_in) p.ws_head[WS_EPOCH] = epoch << kEpochShift;
     }
   }
 }
@@ -538,9 +561,6 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   // pushing launch leaves; it is read AFTER the wait for the previous kernels (a launch may start long before its
   // predecessors are complete), by the roles that store outputs.
   uint32_t push_e = 0u;
-  // Epoch of the {elements, epoch} words that carry r of this launch: the workspace's launch counter + 1, read by the
-  // consumer warps after the same wait.
-  uint32_t r_epoch = 0u;
   // The last n_r_ctas CTAs of the grid only compute r (their copy / aux warps have no tiles): a CTA that ran an R
   // unit AND a full share of row tiles would finish microseconds after the others and set the kernel's length.
   const int n_main = static_cast<int>(gridDim.x) - p.n_r_ctas;
@@ -836,6 +856,8 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     // ================================================================ consumer warps
     const int g = lane >> 2, t = lane & 3;
     bool dep_wait_pending = true;  // x (and a loaded r) come from earlier kernels of the stream
+    uint32_t eword = 0u;           // lane 0: the epoch word as this warp's registration found it
+    uint32_t r_epoch = 0u;         // epoch of the words that carry r of this launch (set at the first L epilogue)
     {
       // Launch parameters live in constant memory, and the first touch of each of their cache lines is a miss of a few
       // hundred cycles: read what the staging and the first tile need NOW, while this CTA waits for the previous kernel
@@ -848,8 +870,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
                    "r"(p.SK), "r"(p.out_fp32), "r"(p.push_world), "l"(p.norm_w));
     }
     if (p.norm_w != nullptr) {     // the row statistics come first: both the R units and the staging need them
-      asm volatile("griddepcontrol.wait;" ::: "memory");
-      dep_wait_pending = false;
+      dep_wait(p, dep_wait_pending, eword);
       norm_stats(p, red, s_rstd);
     }
     if (r_only) {
@@ -860,21 +881,19 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       // the correction (all but slice 0) run the others before their tiles: every unit is then done one round after x
       // is ready, instead of several rounds on the few R CTAs while slice 0 waits for r.
       const bool helped = p.SK > 1 && p.n_r_units > p.n_r_ctas;
-      r_units<NT>(p, bid - n_main, helped ? (1 << 30) : p.n_r_ctas, red, fin, dep_wait_pending,
-                  s_rstd);
+      r_units<NT>(p, bid - n_main, helped ? (1 << 30) : p.n_r_ctas, red, fin, dep_wait_pending, eword, s_rstd);
     } else if (p.r_mode == 1 && p.n_r_ctas > 0 && p.SK > 1 && slice != 0 && p.n_r_units > p.n_r_ctas) {
       const int helpers = (n_main / p.SK) * (p.SK - 1);
       const int idx = (bid / p.SK) * (p.SK - 1) + slice - 1;
-      r_units<NT>(p, p.n_r_ctas + idx, helpers, red, fin, dep_wait_pending, s_rstd);
+      r_units<NT>(p, p.n_r_ctas + idx, helpers, red, fin, dep_wait_pending, eword, s_rstd);
     } else if (p.r_mode == 1 && p.n_r_ctas == 0) {
       // no dedicated CTAs: every CTA takes its share of R units (dealt from the last CTA down) before its tiles
-      r_units<NT>(p, static_cast<int>(gridDim.x) - 1 - bid, static_cast<int>(gridDim.x), red, fin,
-                  dep_wait_pending, s_rstd);
+      r_units<NT>(p, static_cast<int>(gridDim.x) - 1 - bid, static_cast<int>(gridDim.x), red, fin, dep_wait_pending,
+                  eword, s_rstd);
     }
     if (threadIdx.x == 0 && r_only) trace_event(p, 6);
-    if (dep_wait_pending) asm volatile("griddepcontrol.wait;" ::: "memory");
+    dep_wait(p, dep_wait_pending, eword);
     if (p.push_world > 0) push_e = *p.push_epoch + 1u;
-    if (p.r_mode == 1) r_epoch = launch_epoch(p);
     if (threadIdx.x == 0) trace_event(p, 2);
     // per warp: no CTA-wide barrier needed.  A CTA without row tiles (an R CTA of a launch with few tiles) stages
     // nothing and retires: the kernel is complete when its LAST CTA is.
@@ -988,6 +1007,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
         float al[NB][4];
 #pragma unroll
         for (int b = 0; b < NB; ++b) al[b][0] = al[b][1] = al[b][2] = al[b][3] = 0.f;
+        if (!r_ready && p.r_mode == 1) r_epoch = launch_epoch(eword);   // the registration's round trip is long over
         for (int l = 0; l < n_lstages; ++l) {
           ok = ok && mbar_wait_u32(full_u32 + st * 8, ph, cx);
           if (threadIdx.x == 0 && k == 0 && l == 0) trace_event(p, 11);
@@ -1096,15 +1116,13 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
 
   __syncthreads();
   if (threadIdx.x == 0) trace_event(p, 10);
-  if ((p.r_mode == 1 || p.push_world > 0) && threadIdx.x == 0) {
+  if (p.push_world > 0 && threadIdx.x == 0) {
     const uint32_t old = atomicAdd(p.ws_head + WS_EXIT, 1u);
-    if (old == gridDim.x - 1) {  // last CTA out re-arms the counters for the next launch
-      p.ws_head[WS_R_DONE] = 0u;
+    if (old == gridDim.x - 1) {  // last CTA out
       p.ws_head[WS_EXIT] = 0u;
       // every CTA has read the site's call counter by now (each one stamped its stores with counter + 1): advance it
       // for the finishing kernel, which runs after this launch on the same stream
-      if (p.push_world > 0) *p.push_epoch = push_e;
-      if (p.r_mode == 1) p.ws_head[WS_EPOCH] = r_epoch;   // words of this launch never match a later launch's epoch
+      *p.push_epoch = push_e;
       __threadfence();
     }
   }

@@ -41,6 +41,12 @@ inline size_t gemv_smem_layout_bytes(int stages, int meta_gp, int meta_gw, int g
 
 // Workspace header (uint32 words); the rest of the workspace follows at kWsHeaderBytes.
 enum : int { WS_TICKET = 0, WS_R_DONE = 1, WS_EXIT = 2, WS_STATUS = 3, WS_EPOCH = 4, WS_HEADER_WORDS = 64 };
+// WS_EPOCH packs {launch epoch : 20 bits, readers : 12 bits}: every consumer warp of a correcting launch adds 1 when it
+// is past the wait for the previous kernels and takes the epoch from the value the add returns; the CTA that completes
+// r advances the epoch (and clears the readers) once all warps of the grid have registered.
+constexpr int kEpochShift = 12;
+constexpr uint32_t kEpochReaderMask = (1u << kEpochShift) - 1u;
+constexpr uint32_t kEpochMask = (1u << 20) - 1u;
 constexpr size_t kWsHeaderBytes = WS_HEADER_WORDS * 4;
 constexpr int kMaxRTiles = 64;      // rank <= 1024
 // After the header: 256 B of per-R-tile words, then r of the running launch as the row tiles read it - 8-byte words
