@@ -137,6 +137,39 @@ int tensor_map_2d(CUtensorMap* out, CUtensorMapDataType dtype, const void* ptr, 
   return GLOWQ_OK;
 }
 
+// Packed weights for the weight-streaming kernel when the group count is even: [OC rows][G / 2][32 int32], box
+// 32 rows x 4 x 128 B, the shared-memory image swizzled (16-byte chunks XORed within 128 bytes by the 128-byte line
+// index mod 8) so that the consumers' 128-bit loads - eight rows 512 B apart per quarter warp - spread over all
+// banks.  (An odd group count keeps the plain 2-D image: a 128-byte inner box would reach past the last row.)
+int tensor_map_w3d(CUtensorMap* out, const void* ptr, uint64_t group_pairs, uint64_t rows, uint64_t stride_bytes) {
+  const uint64_t groups = group_pairs;
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return GLOWQ_ERR_UNSUPPORTED_DEVICE;
+  const MapKey key{ptr, groups, rows, stride_bytes, kChunkGroups, kTileRows,
+                   static_cast<uint32_t>(CU_TENSOR_MAP_DATA_TYPE_INT32), 2u};
+  size_t h = reinterpret_cast<uintptr_t>(ptr) >> 8;
+  h = (h ^ (h >> 12) ^ (groups * 0x9E3779B97F4A7C15ull) ^ (rows << 7) ^ 0x5bd1e995u) % kMapCacheSlots;
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  MapSlot& slot = g_map_cache[h];
+  if (!(slot.valid && slot.key == key)) {
+    const cuuint64_t dims[3] = {32, group_pairs, rows};
+    const cuuint64_t strides[2] = {128, stride_bytes};
+    const cuuint32_t box[3] = {32, kChunkGroups / 2, kTileRows};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(&slot.map, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      slot.valid = false;
+      return GLOWQ_ERR_CUDA;
+    }
+    slot.key = key;
+    slot.valid = true;
+  }
+  std::memcpy(out, &slot.map, sizeof(CUtensorMap));
+  return GLOWQ_OK;
+}
+
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -417,10 +450,14 @@ int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cuda
       p.l_cols = std::min(std::max(p.rank, 8), 256);
       alignas(64) TensorMaps tm;
       std::memset(&tm, 0, sizeof(tm));
+      p.w_swizzled = (pl.G % 2 == 0) ? 1 : 0;
       for (int i = 0; i < g.n_members; ++i) {
         const MemberDev& d = p.mem[i];
-        int rc = tensor_map_2d(&tm.w[i], CU_TENSOR_MAP_DATA_TYPE_INT32, d.qweight, static_cast<uint64_t>(pl.G) * 16, d.OC,
-                               static_cast<uint64_t>(d.wstride) * 4, kChunkGroups * 16, kTileRows);
+        int rc = p.w_swizzled
+                     ? tensor_map_w3d(&tm.w[i], d.qweight, static_cast<uint64_t>(pl.G / 2), d.OC,
+                                      static_cast<uint64_t>(d.wstride) * 4)
+                     : tensor_map_2d(&tm.w[i], CU_TENSOR_MAP_DATA_TYPE_INT32, d.qweight, static_cast<uint64_t>(pl.G) * 16,
+                                     d.OC, static_cast<uint64_t>(d.wstride) * 4, kChunkGroups * 16, kTileRows);
         if (rc == GLOWQ_OK && d.L != nullptr && p.r_mode != GLOWQ_R_NONE)
           rc = tensor_map_2d(&tm.l[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, d.L, p.rank, d.OC,
                              static_cast<uint64_t>(d.Lstride) * 2, p.l_cols, kTileRows);

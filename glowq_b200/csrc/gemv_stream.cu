@@ -75,11 +75,23 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tmap, 
       "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
       : "memory");
 }
-// L2 prefetch requests (no shared memory involved): the box of a tensor map, or a flat byte range (16-byte aligned
-// address, size a multiple of 16).
+// 3-D form for the packed weights ([rows][group pairs][32 int32], swizzled image): coordinates (0, group / 2, row).
+__device__ __forceinline__ void tma_load_w(void* dst, const CUtensorMap* tmap, int group, int row, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+          smem_u32(dst)),
+      "l"(tmap), "r"(0), "r"(group >> 1), "r"(row), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_w(const CUtensorMap* tmap, int group, int row) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(tmap), "r"(0), "r"(group >> 1), "r"(row)
+               : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* tmap, int x, int y) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
 }
+// L2 prefetch request (no shared memory involved) for a flat byte range (16-byte aligned address, size a multiple
+// of 16).
 __device__ __forceinline__ void l2_prefetch_bytes(const void* p, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
@@ -544,7 +556,8 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   uint64_t* cooked_full = meta_full + kMetaDepth;     // [kCookedDepth]: a tile's converted pairs are written
   uint64_t* cooked_empty = cooked_full + kCookedDepth;  // ... and the consumer warps are done with them
   uint64_t* red_empty = cooked_empty + kCookedDepth;  // the aux warp has drained the reduction buffer
-  unsigned char* ring = smem + 256;
+  // the swizzle of the weight stages works on shared-memory address bits: stages start on 1024-byte boundaries
+  unsigned char* ring = smem + 256 + ((1024u - ((smem_u32(smem) + 256u) & 1023u)) & 1023u);
   const int meta_bytes = kTileRows * (p.meta_gp * 2 + p.meta_gw * 4);
   unsigned char* meta = ring + static_cast<size_t>(p.stages) * kStageBytes;
   const int cooked_bytes = p.gps * (kTileRows * 8);   // [group][row] float2 {scale * 2^24, -scale * zero}
@@ -635,15 +648,21 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
             mbar_arrive(full_bar + st);
           } else {
             mbar_arrive_expect_tx(full_bar + st, kStageBytes);
-            tma_load_2d(ring + static_cast<size_t>(st) * kStageBytes, &tm.w[ti.mi], (g0 + c * kChunkGroups) * 16, ti.row0,
-                        full_bar + st);
+            if (p.w_swizzled)
+              tma_load_w(ring + static_cast<size_t>(st) * kStageBytes, &tm.w[ti.mi], g0 + c * kChunkGroups, ti.row0, full_bar + st);
+            else
+              tma_load_2d(ring + static_cast<size_t>(st) * kStageBytes, &tm.w[ti.mi], (g0 + c * kChunkGroups) * 16, ti.row0,
+                          full_bar + st);
             if (p.deep_prefetch) {
               const int pi = k * n_chunks + c + S;              // weight chunk index (within this CTA) S issues ahead
               const int kp = pi / n_chunks, cp = pi - kp * n_chunks;
               const int tile_p = tile_at(kp);
               if (tile_p < p.n_tiles) {
                 const TileInfo tp_ = tile_info(p, tile_p, slice);
-                tma_prefetch_2d(&tm.w[tp_.mi], (g0 + cp * kChunkGroups) * 16, tp_.row0);
+                if (p.w_swizzled)
+                  tma_prefetch_w(&tm.w[tp_.mi], g0 + cp * kChunkGroups, tp_.row0);
+                else
+                  tma_prefetch_2d(&tm.w[tp_.mi], (g0 + cp * kChunkGroups) * 16, tp_.row0);
               }
             }
           }
@@ -903,7 +922,13 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     // per-lane constant shared addresses: weight quad (warp's group, lane's 16 B, lane's row), x chunk, x sums, the
     // converted scale / zero pairs.  A token slot of the MMA that holds no token reads an all-zero row instead (its
     // address does not advance), so that the loads below are unconditional.
-    const uint32_t ring_lane = smem_u32(ring) + warp * 64 + t * 16 + g * kRowPitch;
+    // Weight stage image: row r of the tile at r * 512 B, group w in its 64 B - with the 16-byte chunks of every
+    // 128 B XORed by (128-byte line index mod 8) = (r & 1) * 4 + w / 2, as the tensor map's swizzle lays them down.
+    // Rows g, g + 8, g + 16, g + 24 share their parity, so the XOR is a per-lane constant.
+    const uint32_t ring_lane =
+        smem_u32(ring) + g * kRowPitch +
+        (p.w_swizzled ? (warp >> 1) * 128 + (((((warp & 1) << 2) | t) ^ (((g & 1) << 2) | (warp >> 1))) << 4)
+                      : warp * 64 + t * 16);
     const uint32_t xsum_lane = smem_u32(xsum) + warp * (32 * NT) + t * 8;
     const uint32_t cooked_lane = smem_u32(cooked) + warp * (kTileRows * 8) + g * 8;
     uint32_t x_lane[NT], x_step[NT];

@@ -28,7 +28,7 @@ constexpr int kZeroRowBytes = 320;  // all-zero activation row for the token slo
 // barriers | weight ring | raw metadata ring | converted metadata ring | reduction buffers | R-unit scratch |
 // x sums | staged x | zero row.
 inline size_t gemv_smem_layout_bytes(int stages, int meta_gp, int meta_gw, int gps, int NT, int M, int xs_stride) {
-  size_t off = 256;
+  size_t off = 256 + 1024;   // barriers, then up to 1 KB of padding: the weight ring starts on a 1024-byte boundary
   off += static_cast<size_t>(stages) * kStageBytes;
   off += static_cast<size_t>(kMetaDepth) * kTileRows * (meta_gp * 2 + meta_gw * 4);
   off += static_cast<size_t>(kCookedDepth) * gps * (kTileRows * 8);
@@ -71,8 +71,9 @@ struct MemberDev {
   int tile_begin;   // index of this member's first row tile (kTileRows rows) in the group's tile list
 };
 
-// TMA descriptors of every member's packed weight ([OC, G*16] int32, box 128 x kTileRows) and left factor
-// ([OC, rank] fp16, box l_cols x kTileRows).  Rows or columns of a box that fall outside the tensor read as zero.
+// TMA descriptors of every member's packed weight ([OC][G/2][32] int32, box kTileRows x kChunkGroups/2 x 32, shared-memory
+// image swizzled within 128 bytes; or [OC][G*16] with box kTileRows x kChunkGroups*16 for an odd group count) and left factor ([OC, rank] fp16, box kTileRows x l_cols).  Rows, groups or columns
+// of a box that fall outside the tensor read as zero.
 struct alignas(64) TensorMaps {
   CUtensorMap w[kMaxMembers];
   CUtensorMap l[kMaxMembers];
@@ -99,6 +100,7 @@ struct GemvParams {
   int l_cols;                    // columns of L per pipeline stage: min(rank, 256)
   int meta_gp, meta_gw;          // per-row metadata pitch: scale halves, zero words (of one K slice)
   int deep_prefetch;             // the copy warp also asks L2 for the chunk that follows S issues later
+  int w_swizzled;                // weight stages arrive swizzled (3-D tensor map, even group count) or as plain rows
   // Byte ranges of the group call that follows on the stream (a prefix of its packed rows in tile order, its right
   // factor): every CTA's copy warp asks L2 for its share once its own copies are issued, so that HBM keeps streaming
   // through this launch's tail and the next launch's prologue.
