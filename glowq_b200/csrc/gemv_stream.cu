@@ -205,7 +205,7 @@ __device__ __forceinline__ void norm_stats(const GemvParams& p, float* part, flo
 // warp + 8, ... of the slice; sixteen lanes per group, two groups per pass), so no warp waits for another one
 // between "x is ready" and its first MMA: a __syncwarp() publishes the data.
 __device__ __forceinline__ void stage_x(const GemvParams& p, int g0, int ng, unsigned char* xs, float* xsum, int mpad,
-                                        const float* s_rstd) {
+                                        const float* s_rstd, bool do_norm) {
   constexpr int kBatch = 4;  // global loads in flight per lane before any of them is consumed
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hsel = lane >> 4, s = lane & 15;   // s = 8-column block of the group, in source order
@@ -226,7 +226,7 @@ __device__ __forceinline__ void stage_x(const GemvParams& p, int g0, int ng, uns
           const __half* src = p.x + static_cast<size_t>(m) * p.x_stride + k;
           if (p.x_vec_ok && k + 8 <= p.IC) {
             v[b] = *reinterpret_cast<const uint4*>(src);
-            if (p.norm_w != nullptr) v[b] = norm_x8(p, v[b], m, k, s_rstd[m]);
+            if (do_norm) v[b] = norm_x8(p, v[b], m, k, s_rstd[m]);
           } else {
             __align__(16) __half tmp[8];
 #pragma unroll
@@ -339,11 +339,11 @@ __device__ __forceinline__ void cross_warp_reduce(float (&acc)[NB][4], float* re
 // The wait for the previous kernels of the stream, once per consumer warp.  In a correcting launch lane 0 then
 // registers the warp as a reader of the workspace's epoch word; the value the add returns (kept in lane 0 until the
 // epoch is needed, so that nobody waits for the round trip here) carries the epoch of the PREVIOUS correcting launch.
-__device__ __forceinline__ void dep_wait(const GemvParams& p, bool& pending, uint32_t& eword) {
+__device__ __forceinline__ void dep_wait(const GemvParams& p, bool& pending, uint32_t& eword, bool computes_r) {
   if (!pending) return;
   asm volatile("griddepcontrol.wait;" ::: "memory");
   pending = false;
-  if (p.r_mode == 1 && (threadIdx.x & 31) == 0) eword = atomicAdd(p.ws_head + WS_EPOCH, 1u);
+  if (computes_r && (threadIdx.x & 31) == 0) eword = atomicAdd(p.ws_head + WS_EPOCH, 1u);
 }
 // Epoch that stamps the words of r in this launch (never 0, the value of a word that was never written).
 __device__ __forceinline__ uint32_t launch_epoch(uint32_t eword) {
@@ -361,7 +361,7 @@ __device__ __forceinline__ uint32_t launch_epoch(uint32_t eword) {
 // flag and no fence on the reading side, and every reader sees the same bits.
 template <int NT>
 __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride, float* red, float* fin,
-                                        bool& dep_wait_pending, uint32_t& eword, const float* s_rstd) {
+                                        bool& dep_wait_pending, uint32_t& eword, const float* s_rstd, bool do_norm) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   if (u0 >= p.n_r_units) return;
   uint4 a[4], b[4];
@@ -403,7 +403,7 @@ __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride
     for (int gl = warp; gl < ng || gl == warp; gl += kConsumerWarps) {
       const bool more_rounds = gl + kConsumerWarps < ng;
       if (gl != warp || unit != u0) load_round(unit, gl, true);
-      dep_wait(p, dep_wait_pending, eword);  // R is static, x is not: the earlier kernels must be complete before x is read
+      dep_wait(p, dep_wait_pending, eword, true);  // R is static, x is not: the earlier kernels must be complete before x is read
       if (gl < ng) {
         const int kb = (gbase + gl) * kGroup + 32 * t;
 #pragma unroll
@@ -427,7 +427,7 @@ __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride
               }
             }
           }
-          if (p.norm_w != nullptr && p.x_vec_ok && tok < p.M) {
+          if (do_norm && p.x_vec_ok && tok < p.M) {
 #pragma unroll
             for (int i = 0; i < 4; ++i)
               if (kb + 8 * i + 8 <= p.IC) xv[i] = norm_x8(p, xv[i], tok, kb + 8 * i, s_rstd[tok]);
@@ -446,7 +446,7 @@ __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride
     for (int e = threadIdx.x; e < NT * 128; e += kConsumerThreads) slot[e] = fin[e];
     ++n_done;
   }
-  dep_wait(p, dep_wait_pending, eword);
+  dep_wait(p, dep_wait_pending, eword, true);
   consumer_sync();
   uint32_t* last_flag = reinterpret_cast<uint32_t*>(fin);   // fin is free again
   if (threadIdx.x == 0) {
@@ -525,7 +525,7 @@ struct TileInfo {
   int mi, row0;
   bool corr;
 };
-__device__ __forceinline__ TileInfo tile_info(const GemvParams& p, int tile, int slice) {
+__device__ __forceinline__ TileInfo tile_info(const GemvParams& p, int tile, int slice, int r_mode) {
   int mi = 0;
 #pragma unroll
   for (int i = 1; i < kMaxMembers; ++i)
@@ -533,16 +533,25 @@ __device__ __forceinline__ TileInfo tile_info(const GemvParams& p, int tile, int
   TileInfo ti;
   ti.mi = mi;
   ti.row0 = (tile - p.mem[mi].tile_begin) * kTileRows;
-  ti.corr = (slice == 0) && (p.r_mode != 0) && (p.mem[mi].L != nullptr) && (p.mem[mi].alpha != 0.f);
+  ti.corr = (slice == 0) && (r_mode != 0) && (p.mem[mi].L != nullptr) && (p.mem[mi].alpha != 0.f);
   return ti;
 }
 
 #ifndef GLOWQ_GEMV_MIN_CTAS
 #define GLOWQ_GEMV_MIN_CTAS 2   // CTAs per SM the register allocation is bounded for
 #endif
-template <int NT>
+// FEAT selects what is compiled in: bit 0 the low-rank correction, bit 1 K slices, bit 2 the optional extras (fused
+// input transform, tensor-parallel push).  A launch takes the smallest instantiation the host offers that covers
+// it: the code of features that are switched off costs instruction-cache misses and predicated instructions on every
+// launch (the everything-in instantiation is 1.6 times the size of the corrected one and measured 3 % slower on it).
+enum : int { kFeatCorr = 1, kFeatSliced = 2, kFeatExtras = 4 };
+template <int NT, int FEAT>
 __global__ void __launch_bounds__(kGemvThreads, (NT <= 2) ? GLOWQ_GEMV_MIN_CTAS : 1)
 gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__ TensorMaps tm) {
+  const int r_mode = (FEAT & kFeatCorr) ? p.r_mode : 0;
+  const int SK = (FEAT & kFeatSliced) ? p.SK : 1;
+  const int push_world = (FEAT & kFeatExtras) ? p.push_world : 0;
+  const __half* const norm_w = (FEAT & kFeatExtras) ? p.norm_w : nullptr;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_abort;
   __shared__ float s_rstd[8];   // fused RMSNorm: 1 / rms of every token row
@@ -583,13 +592,13 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   const int bid = static_cast<int>(blockIdx.x) >= p.n_r_ctas ? static_cast<int>(blockIdx.x) - p.n_r_ctas
                                                              : n_main + static_cast<int>(blockIdx.x);
   const bool r_only = bid >= n_main;
-  const int slice = bid % p.SK;
-  const int first_tile = r_only ? p.n_tiles : bid / p.SK;
-  const int tile_step = n_main / p.SK;
+  const int slice = bid % SK;
+  const int first_tile = r_only ? p.n_tiles : bid / SK;
+  const int tile_step = n_main / SK;
   // k-th row tile of this CTA (>= n_tiles: none left).  With K slices every CTA of a slice strides over the tiles.
   // Without, the first round of tiles goes to the main CTAs only and the rest is dealt over ALL CTAs, so that the
   // CTAs that computed r pick up row tiles afterwards instead of idling through a long launch.
-  const bool deal_all = (p.SK == 1 && p.n_r_ctas > 0);
+  const bool deal_all = (SK == 1 && p.n_r_ctas > 0);
   // The leftover tiles are dealt in the order [R CTAs, main CTAs]: an R CTA is free again about two microseconds
   // into the launch, a main CTA only after its first tile.
   auto tile_at = [&](int k) -> int {
@@ -636,7 +645,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     uint32_t st = 0, ph = 0, issued = 0;
     bool ok = true;
     for (int k = 0, tile; (tile = tile_at(k)) < p.n_tiles && ok; ++k) {
-      const TileInfo ti = tile_info(p, tile, slice);
+      const TileInfo ti = tile_info(p, tile, slice, r_mode);
       // L2 lookahead: with every weight chunk handed to the ring, the chunk that will follow S issues later (a later
       // chunk of this tile or one of the CTA's next tiles) is requested from L2.  The ring is only S stages deep, so
       // at the start of a launch - all slots filled, consumers still waiting for x - the chunks beyond it would
@@ -658,7 +667,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
               const int kp = pi / n_chunks, cp = pi - kp * n_chunks;
               const int tile_p = tile_at(kp);
               if (tile_p < p.n_tiles) {
-                const TileInfo tp_ = tile_info(p, tile_p, slice);
+                const TileInfo tp_ = tile_info(p, tile_p, slice, r_mode);
                 if (p.w_swizzled)
                   tma_prefetch_w(&tm.w[tp_.mi], g0 + cp * kChunkGroups, tp_.row0);
                 else
@@ -725,7 +734,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     bool ok = true;
     auto prefetch_raw = [&]() {
       const int tile_m = tile_at(k_m);
-      const TileInfo tm_i = tile_info(p, tile_m, slice);
+      const TileInfo tm_i = tile_info(p, tile_m, slice, r_mode);
       const MemberDev& mbm = p.mem[tm_i.mi];
       const uint32_t slot = static_cast<uint32_t>(k_m % kMetaDepth);
       const int row = min(tm_i.row0 + lane, mbm.OC - 1);
@@ -782,14 +791,14 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       if (k_m == k + kMetaDepth && tile_at(k_m) < p.n_tiles) prefetch_raw();
       const bool last = tile_at(k + 1) >= p.n_tiles;
       if (!last) cook(k + 1);
-      if (last && p.SK == 1) break;   // the consumer warps finish this tile themselves
+      if (last && SK == 1) break;   // the consumer warps finish this tile themselves
 
       // ---- epilogue of `tile` (outputs may still be read by the previous kernel until it has completed)
       if (k == 0) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        if (p.push_world > 0) push_e = *p.push_epoch + 1u;
+        if (push_world > 0) push_e = *p.push_epoch + 1u;
       }
-      const TileInfo ti = tile_info(p, tile, slice);
+      const TileInfo ti = tile_info(p, tile, slice, r_mode);
       const MemberDev& mb = p.mem[ti.mi];
       if (buf == 0)
         asm volatile("bar.sync 2, %0;" ::"n"(kConsumerThreads + 32) : "memory");
@@ -813,15 +822,15 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       if (lane == 0) mbar_arrive(red_empty);  // the consumers may refill the buffer
       buf ^= 1;                               // (the named barriers alternate)
       bool finalize = true;
-      if (p.SK > 1) {
+      if (SK > 1) {
         // every K slice parks its tile; the last slice to arrive adds them up in slice order (deterministic)
-        float4* part = reinterpret_cast<float4*>(p.sk_partial + static_cast<size_t>(tile) * p.SK * (NB * 128));
+        float4* part = reinterpret_cast<float4*>(p.sk_partial + static_cast<size_t>(tile) * SK * (NB * 128));
 #pragma unroll
         for (int b = 0; b < NB; ++b) part[static_cast<size_t>(slice) * (NB * 32) + b * 32 + lane] = v[b];
         __threadfence();
         __syncwarp();
         int last = 0;
-        if (lane == 0) last = (atomicAdd(p.tile_ctr + tile, 1u) == static_cast<uint32_t>(p.SK - 1));
+        if (lane == 0) last = (atomicAdd(p.tile_ctr + tile, 1u) == static_cast<uint32_t>(SK - 1));
         last = __shfl_sync(0xffffffffu, last, 0);
         finalize = (last != 0);
         if (finalize) {
@@ -829,7 +838,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
 #pragma unroll
           for (int b = 0; b < NB; ++b) {
             float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int k = 0; k < p.SK; ++k) {
+            for (int k = 0; k < SK; ++k) {
               const float4 q = __ldcg(part + static_cast<size_t>(k) * (NB * 32) + b * 32 + lane);
               s4.x += q.x;
               s4.y += q.y;
@@ -862,7 +871,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
                 const __half h = __float2half_rn(o);
                 static_cast<__half*>(mb.out)[idx] = h;
                 // one 8-byte peer store per rank: {value, epoch} (out_stride == OC, so idx is the dense index)
-                for (int r = 0; r < p.push_world; ++r) p.push_slot[r][idx] = make_uint2(__half_as_ushort(h), push_e);
+                for (int r = 0; r < push_world; ++r) p.push_slot[r][idx] = make_uint2(__half_as_ushort(h), push_e);
               }
             }
           }
@@ -882,41 +891,43 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       // hundred cycles: read what the staging and the first tile need NOW, while this CTA waits for the previous kernel
       // anyway, instead of one miss after another on the path from "x is ready" to the first MMA.
       const int t0 = tile_at(0);
-      const TileInfo tf = tile_info(p, t0 < p.n_tiles ? t0 : 0, slice);
+      const TileInfo tf = tile_info(p, t0 < p.n_tiles ? t0 : 0, slice, r_mode);
       const MemberDev& m0 = p.mem[tf.mi];
       asm volatile("" ::"r"(m0.OC), "r"(m0.out_stride), "f"(m0.alpha), "l"(m0.bias), "l"(m0.out), "l"(m0.L), "r"(p.M),
-                   "r"(p.xs_stride), "r"(p.rank), "r"(p.r_mode), "l"(p.x), "r"(p.x_stride), "r"(p.IC), "r"(p.x_vec_ok),
-                   "r"(p.SK), "r"(p.out_fp32), "r"(p.push_world), "l"(p.norm_w));
+                   "r"(p.xs_stride), "r"(p.rank), "r"(r_mode), "l"(p.x), "r"(p.x_stride), "r"(p.IC), "r"(p.x_vec_ok),
+                   "r"(SK), "r"(p.out_fp32), "r"(push_world), "l"(norm_w));
     }
-    if (p.norm_w != nullptr) {     // the row statistics come first: both the R units and the staging need them
-      dep_wait(p, dep_wait_pending, eword);
+    if (norm_w != nullptr) {     // the row statistics come first: both the R units and the staging need them
+      dep_wait(p, dep_wait_pending, eword, r_mode == 1);
       norm_stats(p, red, s_rstd);
     }
+    // R units of this CTA (first unit, stride; none if ru0 < 0).  The grid is persistent - never larger than what is
+    // resident at once - so every unit's owner is running while the other CTAs wait (bounded) for r before their first
+    // L epilogue.  R loads go out before the dependency wait; x is staged only afterwards, for the row tiles the CTA
+    // picks up later.  With K slices and more units than R CTAs, an R CTA runs ONE unit and the CTAs of the slices
+    // that do not apply the correction (all but slice 0) run the others before their tiles: every unit is then done
+    // one round after x is ready, instead of several rounds on the few R CTAs while slice 0 waits for r.  Without
+    // dedicated CTAs every CTA takes its share (dealt from the last CTA down) before its tiles.
+    int ru0 = -1, rstride = 1;
     if (r_only) {
-      // The grid is persistent - never larger than what is resident at once - so every unit's owner is running
-      // while the other CTAs wait (bounded) for r before their first L epilogue.  R loads go out before the
-      // dependency wait; x is staged only afterwards, for the row tiles this CTA picks up later.
-      // With K slices and more units than R CTAs, an R CTA runs ONE unit and the CTAs of the slices that do not apply
-      // the correction (all but slice 0) run the others before their tiles: every unit is then done one round after x
-      // is ready, instead of several rounds on the few R CTAs while slice 0 waits for r.
-      const bool helped = p.SK > 1 && p.n_r_units > p.n_r_ctas;
-      r_units<NT>(p, bid - n_main, helped ? (1 << 30) : p.n_r_ctas, red, fin, dep_wait_pending, eword, s_rstd);
-    } else if (p.r_mode == 1 && p.n_r_ctas > 0 && p.SK > 1 && slice != 0 && p.n_r_units > p.n_r_ctas) {
-      const int helpers = (n_main / p.SK) * (p.SK - 1);
-      const int idx = (bid / p.SK) * (p.SK - 1) + slice - 1;
-      r_units<NT>(p, p.n_r_ctas + idx, helpers, red, fin, dep_wait_pending, eword, s_rstd);
-    } else if (p.r_mode == 1 && p.n_r_ctas == 0) {
-      // no dedicated CTAs: every CTA takes its share of R units (dealt from the last CTA down) before its tiles
-      r_units<NT>(p, static_cast<int>(gridDim.x) - 1 - bid, static_cast<int>(gridDim.x), red, fin, dep_wait_pending,
-                  eword, s_rstd);
+      ru0 = bid - n_main;
+      rstride = (SK > 1 && p.n_r_units > p.n_r_ctas) ? (1 << 30) : p.n_r_ctas;
+    } else if (r_mode == 1 && p.n_r_ctas > 0 && SK > 1 && slice != 0 && p.n_r_units > p.n_r_ctas) {
+      ru0 = p.n_r_ctas + (bid / SK) * (SK - 1) + slice - 1;
+      rstride = (n_main / SK) * (SK - 1);
+    } else if (r_mode == 1 && p.n_r_ctas == 0) {
+      ru0 = static_cast<int>(gridDim.x) - 1 - bid;
+      rstride = static_cast<int>(gridDim.x);
     }
+    if (r_mode == 1 && ru0 >= 0)
+      r_units<NT>(p, ru0, rstride, red, fin, dep_wait_pending, eword, s_rstd, norm_w != nullptr);
     if (threadIdx.x == 0 && r_only) trace_event(p, 6);
-    dep_wait(p, dep_wait_pending, eword);
-    if (p.push_world > 0) push_e = *p.push_epoch + 1u;
+    dep_wait(p, dep_wait_pending, eword, r_mode == 1);
+    if (push_world > 0) push_e = *p.push_epoch + 1u;
     if (threadIdx.x == 0) trace_event(p, 2);
     // per warp: no CTA-wide barrier needed.  A CTA without row tiles (an R CTA of a launch with few tiles) stages
     // nothing and retires: the kernel is complete when its LAST CTA is.
-    if (tile_at(0) < p.n_tiles) stage_x(p, g0, ng, xs, xsum, 8 * NT, s_rstd);
+    if (tile_at(0) < p.n_tiles) stage_x(p, g0, ng, xs, xsum, 8 * NT, s_rstd, norm_w != nullptr);
     if (threadIdx.x == 0) trace_event(p, 3);
 
     // per-lane constant shared addresses: weight quad (warp's group, lane's 16 B, lane's row), x chunk, x sums, the
@@ -941,10 +952,10 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     }
 
     uint32_t st = 0, ph = 0, rbuf = 0, rph = 0;
-    bool ok = true, r_ready = (p.r_mode != 1), rb_cached = false;
+    bool ok = true, r_ready = (r_mode != 1), rb_cached = false;
     uint4 rb_keep[NT];  // r fragments of this lane (first L stage): the same for every row tile of the CTA
     for (int k = 0, tile; (tile = tile_at(k)) < p.n_tiles; ++k) {
-      const TileInfo ti = tile_info(p, tile, slice);
+      const TileInfo ti = tile_info(p, tile, slice, r_mode);
       const MemberDev& mb = p.mem[ti.mi];
       const uint32_t cslot = static_cast<uint32_t>(k % kCookedDepth), cph = static_cast<uint32_t>(k / kCookedDepth) & 1u;
       ok = ok && mbar_wait_u32(cfull_u32 + cslot * 8, cph, cx);
@@ -1032,7 +1043,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
         float al[NB][4];
 #pragma unroll
         for (int b = 0; b < NB; ++b) al[b][0] = al[b][1] = al[b][2] = al[b][3] = 0.f;
-        if (!r_ready && p.r_mode == 1) r_epoch = launch_epoch(eword);   // the registration's round trip is long over
+        if (!r_ready && r_mode == 1) r_epoch = launch_epoch(eword);   // the registration's round trip is long over
         for (int l = 0; l < n_lstages; ++l) {
           ok = ok && mbar_wait_u32(full_u32 + st * 8, ph, cx);
           if (threadIdx.x == 0 && k == 0 && l == 0) trace_event(p, 11);
@@ -1051,7 +1062,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
               for (int nt = 0; nt < NT; ++nt) {
                 if (!(kin && tokv[nt])) {
                   rb[nt] = make_uint4(0, 0, 0, 0);
-                } else if (p.r_mode != 1) {
+                } else if (r_mode != 1) {
                   rb[nt] = ldg_cg_v4(p.r_buf + static_cast<size_t>(nt * 8 + g) * p.rank + 256 * l + k);
                 } else {
                   rb[nt] = r_frag_poll(p, nt * 8 + g, 256 * l + k, r_epoch, &s_abort);
@@ -1100,7 +1111,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
         for (int b = 0; b < NB; ++b)
           red4[(warp * NB + b) * 32 + lane] = make_float4(acc[b][0], acc[b][1], acc[b][2], acc[b][3]);
       }
-      if (p.SK == 1 && tile_at(k + 1) >= p.n_tiles) {
+      if (SK == 1 && tile_at(k + 1) >= p.n_tiles) {
         // This CTA's last tile (K not sliced): nothing is left to overlap with, so the 256 consumer threads add the
         // eight partial sums themselves - one output element each per fragment block - instead of handing the
         // tile to the single aux warp.
@@ -1122,7 +1133,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
             } else {
               const __half h = __float2half_rn(o);
               static_cast<__half*>(mb.out)[idx] = h;
-              for (int r = 0; r < p.push_world; ++r) p.push_slot[r][idx] = make_uint2(__half_as_ushort(h), push_e);
+              for (int r = 0; r < push_world; ++r) p.push_slot[r][idx] = make_uint2(__half_as_ushort(h), push_e);
             }
           }
         }
@@ -1141,7 +1152,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
 
   __syncthreads();
   if (threadIdx.x == 0) trace_event(p, 10);
-  if (p.push_world > 0 && threadIdx.x == 0) {
+  if (push_world > 0 && threadIdx.x == 0) {
     const uint32_t old = atomicAdd(p.ws_head + WS_EXIT, 1u);
     if (old == gridDim.x - 1) {  // last CTA out
       p.ws_head[WS_EXIT] = 0u;
@@ -1221,13 +1232,13 @@ size_t gemv_smem_bytes(const GemvParams& p, int NT) {
   return gemv_smem_layout_bytes(p.stages, p.meta_gp, p.meta_gw, p.gps, NT, p.M, p.xs_stride);
 }
 
-template <int NT>
-static cudaError_t launch_nt(const GemvParams& p, const TensorMaps& tm, int grid, cudaStream_t stream) {
+template <int FEAT>
+static cudaError_t launch_feat(const GemvParams& p, const TensorMaps& tm, int grid, cudaStream_t stream) {
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<1, FEAT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
     if (e != cudaSuccess) return e;
     attr_done[dev] = true;
   }
@@ -1238,21 +1249,31 @@ static cudaError_t launch_nt(const GemvParams& p, const TensorMaps& tm, int grid
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kGemvThreads);
-  cfg.dynamicSmemBytes = gemv_smem_bytes(p, NT);
+  cfg.dynamicSmemBytes = gemv_smem_bytes(p, 1);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = use_pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<NT>, p, tm);
+  return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<1, FEAT>, p, tm);
 }
 
 cudaError_t launch_gemv_stream(const GemvParams& p, const TensorMaps& tm, int NT, int grid, cudaStream_t stream) {
   // Launches carry at most 8 tokens (one token block): wider instantiations measured 3-13x slower per token than
   // repeated 8-token launches, so the host splits larger batches or takes the tensor-core GEMM.
   if (NT != 1) return cudaErrorInvalidValue;
-  return launch_nt<1>(p, tm, grid, stream);
+  // K slices stay a run-time property of every instantiation: a decode step mixes sliced (down_proj) and unsliced
+  // launches, and alternating between two kernels costs more than the slicing code does (the instruction cache stays
+  // warm across back-to-back launches of ONE function: 2.44 against 2.53 ms per Llama-2-13B token step).
+  const int feat = (p.r_mode != 0 ? kFeatCorr : 0) | kFeatSliced |
+                   ((p.push_world > 0 || p.norm_w != nullptr) ? kFeatExtras : 0);
+  switch (feat) {
+    case kFeatSliced: return launch_feat<kFeatSliced>(p, tm, grid, stream);
+    case kFeatSliced | kFeatCorr: return launch_feat<kFeatSliced | kFeatCorr>(p, tm, grid, stream);
+    case kFeatSliced | kFeatExtras: return launch_feat<kFeatSliced | kFeatExtras>(p, tm, grid, stream);
+    default: return launch_feat<kFeatSliced | kFeatCorr | kFeatExtras>(p, tm, grid, stream);
+  }
 }
 
 cudaError_t launch_generic_r(const __half* x, const __half* R, __half* r_buf, float* r32, int r_mode, int M, int IC,
