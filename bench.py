@@ -47,9 +47,8 @@ def parse_args():
                          "NCCL all-reduces between per-segment graphs")
     ap.add_argument("--push", default="auto", choices=["auto", "on", "off"],
                     help="with N > 1: let the row-split linears store their partial sums to the peers from their own "
-                         "epilogue (group.push + the finishing kernel) instead of the one-launch peer all-reduce. "
-                         "auto: for one or two tokens, where it measured ahead (8-byte words per element cost more "
-                         "than they save from a handful of tokens on)")
+                         "epilogue and complete the sum in their last CTAs (group.push) instead of the one-launch peer "
+                         "all-reduce that follows them. auto: wherever the launch can (up to 8 tokens)")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the extra `sweep` and `e2e_host_entry` measurements")
@@ -290,9 +289,7 @@ class GpuArm:
             def step():
                 for i, (arr, n, t) in enumerate(segs):
                     check(lib.glowq_w4a16_group_forward_many(arr, n), "group_forward_many")
-                    if pushed:
-                        self.peer_ar.finish(t, site=i & 1)
-                    else:
+                    if not pushed:   # a pushing launch completes the sum itself
                         self.peer_ar.all_reduce(t, site=i & 1)
             return step, None
 
@@ -357,7 +354,7 @@ class GpuArm:
         """Whether the row-split launches of an M-token step store to the peers themselves."""
         if self.world == 1 or self.peer_ar is None or self.args.push == "off":
             return False
-        return M <= (2 if self.args.push == "auto" else 8)
+        return M <= 8   # the weight-streaming kernel's launches; larger batches take the GEMM and the separate all-reduce
 
     def decode(self, stack, M, steps, warmup, corrected=True):
         """Time one decode configuration; returns (ms per step, run callable, plan)."""
@@ -486,7 +483,7 @@ def run_gpu(args, shape):
             "vs_baseline": None, "dtype": "f32 accumulate over fp16 x int4 (tensor-core MMA), fp16 out",
             "data": "synthetic", "config": workload_config(args, shape),
             "plan": {"parallelism": f"tp{world}", "cuda_graph": use_graph,
-                     "collective": ((("peer stores from the row-split launch + finishing kernel" if arm.pushes(M)
+                     "collective": ((("inside the row-split launch (peer stores from its epilogue, summed by its last CTAs)" if arm.pushes(M)
                                       else "peer-store all-reduce kernel") if arm.peer_ar is not None else "nccl")
                                     if world > 1 else None),
                      "launches_per_layer": calls_per_layer},

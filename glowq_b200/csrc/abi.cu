@@ -20,6 +20,7 @@ cudaError_t launch_dequant(const int32_t* qweight, const __half* scales, const i
                            int group_size, int wstride, int zstride, int sstride, cudaStream_t stream);
 bool gemm_supported(const glowq_w4a16_group_t& g);
 size_t gemm_workspace_bytes(int M, int IC, int OC_total, int rank, int n_members);
+unsigned allreduce_spin_limit();
 int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaError_t* cuda_err);
 }  // namespace glowq
 
@@ -423,6 +424,9 @@ int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cuda
       const size_t slot = (static_cast<size_t>(g.push_site) * pp.world + pp.rank) * pp.max_n;
       for (int r = 0; r < pp.world; ++r) p.push_slot[r] = static_cast<uint2*>(pp.ll_buf[r]) + slot;
       p.push_epoch = static_cast<uint32_t*>(pp.epoch) + g.push_site;
+      p.push_local = static_cast<const uint2*>(pp.ll_buf[pp.rank]) + static_cast<size_t>(g.push_site) * pp.world * pp.max_n;
+      p.push_max_n = pp.max_n;
+      p.push_spin = allreduce_spin_limit();
     }
 
     cudaError_t e;

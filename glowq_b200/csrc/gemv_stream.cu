@@ -44,6 +44,7 @@ constexpr int kConsumerThreads = kConsumerWarps * 32;
 // milliseconds behind.  The drain loop after a failure uses the short limit below.
 constexpr uint32_t kMbarSpinLimit = 1u << 20;
 constexpr uint32_t kDrainSpinLimit = 1u << 12;
+constexpr int kPushFinishers = 16;         // CTAs that complete a pushing launch's all-reduce
 constexpr uint32_t kSuspendHintNs = 2000;  // a waiting thread sleeps in hardware instead of burning issue slots
 
 // ---------------------------------------------------------------- mbarrier / bulk-copy primitives
@@ -869,8 +870,10 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
                 static_cast<float*>(mb.out)[idx] = o;
               } else {
                 const __half h = __float2half_rn(o);
-                static_cast<__half*>(mb.out)[idx] = h;
-                // one 8-byte peer store per rank: {value, epoch} (out_stride == OC, so idx is the dense index)
+                if (push_world == 0) static_cast<__half*>(mb.out)[idx] = h;
+                // pushing: one 8-byte store per rank, {value, epoch} (out_stride == OC, so idx is the dense index);
+                // the output itself is written by the CTAs that add up the ranks' words at the end of the launch
+#pragma unroll 1
                 for (int r = 0; r < push_world; ++r) p.push_slot[r][idx] = make_uint2(__half_as_ushort(h), push_e);
               }
             }
@@ -1132,7 +1135,8 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
               static_cast<float*>(mb.out)[idx] = o;
             } else {
               const __half h = __float2half_rn(o);
-              static_cast<__half*>(mb.out)[idx] = h;
+              if (push_world == 0) static_cast<__half*>(mb.out)[idx] = h;
+#pragma unroll 1
               for (int r = 0; r < push_world; ++r) p.push_slot[r][idx] = make_uint2(__half_as_ushort(h), push_e);
             }
           }
@@ -1152,13 +1156,49 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
 
   __syncthreads();
   if (threadIdx.x == 0) trace_event(p, 10);
-  if (push_world > 0 && threadIdx.x == 0) {
-    const uint32_t old = atomicAdd(p.ws_head + WS_EXIT, 1u);
-    if (old == gridDim.x - 1) {  // last CTA out
+  if (push_world > 0) {
+    // The all-reduce completes inside the launch: CTAs take a ticket when their tiles are stored, and the last few
+    // each poll a share of the output's words - every rank's, this one's included - in this rank's buffer until they
+    // carry the call's epoch (bounded), add the ranks' values in rank order (fp32, the same order everywhere, so every
+    // rank holds the same bits) and write the sum.  All words of an element are requested before the first is tested.
+    __shared__ uint32_t s_ticket, s_epoch;
+    if (threadIdx.x == 0) {
+      s_ticket = atomicAdd(p.ws_head + WS_EXIT, 1u);
+      s_epoch = push_e;
+    }
+    __syncthreads();
+    const int ticket = static_cast<int>(s_ticket);
+    const uint32_t e = s_epoch;
+    const int nfin = min(kPushFinishers, static_cast<int>(gridDim.x)), first = static_cast<int>(gridDim.x) - nfin;
+    if (ticket >= first) {
+      const int n = p.M * p.mem[0].OC;
+      __half* out = static_cast<__half*>(p.mem[0].out);
+      for (int i = (ticket - first) * kGemvThreads + static_cast<int>(threadIdx.x); i < n; i += nfin * kGemvThreads) {
+        uint2 w[kMaxRanks];
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+          if (r < push_world) w[r] = ld_volatile_v2(p.push_local + static_cast<size_t>(r) * p.push_max_n + i);
+        float acc = 0.f;
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+          if (r < push_world) {
+            unsigned spins = 0;
+            while (w[r].y != e) {
+              if (++spins > p.push_spin) {
+                atomicExch(p.ws_head + WS_STATUS, 4u);
+                break;
+              }
+              w[r] = ld_volatile_v2(p.push_local + static_cast<size_t>(r) * p.push_max_n + i);
+            }
+            acc += __half2float(__ushort_as_half(static_cast<unsigned short>(w[r].x)));
+          }
+        out[i] = __float2half_rn(acc);
+      }
+    }
+    if (ticket == static_cast<int>(gridDim.x) - 1 && threadIdx.x == 0) {
+      // every CTA has taken its ticket, so every CTA has read the site's call counter: advance it for the next call
       p.ws_head[WS_EXIT] = 0u;
-      // every CTA has read the site's call counter by now (each one stamped its stores with counter + 1): advance it
-      // for the finishing kernel, which runs after this launch on the same stream
-      *p.push_epoch = push_e;
+      *p.push_epoch = e;
       __threadfence();
     }
   }

@@ -113,10 +113,14 @@ struct GemvParams {
   __half* hidden_out;
   float norm_eps;
   // Tensor-parallel push (row-split linears): push_slot[r] = rank r's staging slot for THIS rank's partial result
-  // ([M][OC] 8-byte words {fp16 value, epoch}), push_epoch = local call counter of the site.  push_world == 0: none.
+  // ([M][OC] 8-byte words {fp16 value, epoch}), push_epoch = local call counter of the site.  The last CTAs to finish
+  // their tiles poll the local word buffer and write the sum over the ranks to the output.  push_world == 0: none.
   int push_world;
   uint2* push_slot[kMaxRanks];
   uint32_t* push_epoch;
+  const uint2* push_local;       // this rank's word buffer of the site: [world][push_max_n]
+  int push_max_n;
+  unsigned push_spin;            // polls of one word before the launch gives up (status 4)
   MemberDev mem[kMaxMembers];
 };
 

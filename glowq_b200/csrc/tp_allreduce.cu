@@ -30,6 +30,10 @@ unsigned ar_spin_limit() {
   return v;
 }
 
+}  // namespace
+unsigned allreduce_spin_limit() { return ar_spin_limit(); }
+namespace {
+
 struct ArParams {
   const uint2* ll_local;                 // finish only: this rank's word buffer [sites][world][max_n] {value, epoch}
   unsigned char* buf[GLOWQ_MAX_RANKS];   // staging buffer of every rank: [sites][world][max_n] fp16
@@ -74,21 +78,24 @@ __global__ void __launch_bounds__(kArThreads) allreduce_push_kernel(const __grid
     const uint2* mine = p.ll_local + static_cast<size_t>(p.site) * p.world * p.max_n;
     __half* dst = p.inout;
     for (int i = threadIdx.x; i < p.n; i += kArThreads) {
+      uint2 w[GLOWQ_MAX_RANKS];   // all ranks' words are requested before the first one is tested
+#pragma unroll
+      for (int r = 0; r < GLOWQ_MAX_RANKS; ++r)
+        if (r < p.world) w[r] = ld_volatile_v2(mine + static_cast<size_t>(r) * p.max_n + i);
       float acc = 0.f;
-      for (int r = 0; r < p.world; ++r) {
-        const uint2* w = mine + static_cast<size_t>(r) * p.max_n + i;
-        uint2 v;
-        unsigned spins = 0;
-        for (;;) {
-          asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(w) : "memory");
-          if (v.y == e) break;
-          if (++spins > p.spin_limit) {
-            atomicExch(p.status, 4u);
-            break;
+#pragma unroll
+      for (int r = 0; r < GLOWQ_MAX_RANKS; ++r)
+        if (r < p.world) {
+          unsigned spins = 0;
+          while (w[r].y != e) {
+            if (++spins > p.spin_limit) {
+              atomicExch(p.status, 4u);
+              break;
+            }
+            w[r] = ld_volatile_v2(mine + static_cast<size_t>(r) * p.max_n + i);
           }
+          acc += __half2float(__ushort_as_half(static_cast<unsigned short>(w[r].x)));
         }
-        acc += __half2float(__ushort_as_half(static_cast<unsigned short>(v.x)));
-      }
       dst[i] = __float2half_rn(acc);
     }
     return;

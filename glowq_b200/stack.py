@@ -204,7 +204,7 @@ class LinearStack:
              out_dtype: int = K.OUT_F16, split_k: int = 0, chain: bool = True, push=None):
         """Build (once per configuration) the ctypes array of group calls for one token step of M tokens."""
         # push: a glowq_b200.tp.PeerAllReduce - the row-split groups (o_proj, down_proj) then store their partial result
-        # into every rank's staging slot themselves (sites alternate), to be completed by push.finish(out, site)
+        # into every rank's staging slot themselves (sites alternate) and write the sum over the ranks to their output
         key = (M, corrected, fuse_groups, kernel, out_dtype, split_k, chain, id(push))
         if key in self._plans:
             return self._plans[key]

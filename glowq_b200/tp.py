@@ -140,12 +140,13 @@ class PeerAllReduce:
 
     def descriptor_address(self) -> int:
         """Address of the ``glowq_w4a16_peers_t`` (for ``Group.push``: the row-split launch stores its result into every
-        rank's slot itself; complete with :meth:`finish`)."""
+        rank's slot itself and its last CTAs write the sum over the ranks to the output)."""
         import ctypes
         return ctypes.addressof(self.peers)
 
     def finish(self, out: torch.Tensor, site: int) -> torch.Tensor:
-        """Second half after a pushing launch on ``site``: wait for every rank's flag and write the sum to ``out``."""
+        """Sum of the words a pushing launch on ``site`` left in this rank's buffer, written to ``out``.  The launch does
+        this itself; the call remains for callers that want the sum in another buffer, and reproduces the same bits."""
         if out.dtype != torch.float16 or not out.is_contiguous() or out.numel() % 8:
             raise ValueError("expected a contiguous fp16 tensor with a multiple of 8 elements")
         rc = self.ext.lib.glowq_w4a16_allreduce_finish_f16(self.peers, out.data_ptr(), out.numel(), int(site),

@@ -104,13 +104,15 @@ typedef struct glowq_w4a16_group {
    * Nothing is computed for `next`, and a wrong hint costs bandwidth, not correctness.  The reference has
    * no counterpart (its launches are independent: csrc/gemv_w4a16.cu:194-211). */
   const struct glowq_w4a16_group* next;
-  /* Optional, tensor-parallel row-split linears (o_proj, down_proj shards): besides writing `out`, the launch stores
-   * its result - this rank's partial sum - into slot [push_site][rank] of EVERY rank's `ll_buf` as its tiles finish,
-   * each element as one 8-byte word {value, epoch}: the first half of glowq_w4a16_allreduce_f16 without a launch of
-   * its own, without fences and without flags.  glowq_w4a16_allreduce_finish_f16 (same peers, same site) polls the
-   * words of all ranks' slots until they carry the call's epoch and adds them.  Requirements: one member, fp16 output, out_stride == OC,
-   * M * OC <= peers->max_n and a multiple of 8, M <= 8 (the weight-streaming kernel); GLOWQ_ERR_UNSUPPORTED_SHAPE
-   * otherwise.  NULL = no push.  See glowq_w4a16_peers_t below for the buffers. */
+  /* Optional, tensor-parallel row-split linears (o_proj, down_proj shards): the launch performs the all-reduce of its
+   * result itself.  As its tiles finish it stores this rank's partial sums into slot [push_site][rank] of EVERY rank's
+   * `ll_buf`, each element as one 8-byte word {value, epoch} (no fences, no flags), and its last CTAs poll - bounded,
+   * status 4 in the workspace on expiry - the words of all ranks' slots in the local `ll_buf`, add them in rank order
+   * (fp32) and write the fp16 sums to `out`: when the launch is complete, `out` holds the same bits on every rank.
+   * Every rank issues the same call; a site may be reused once the call on the other site has been issued.
+   * Requirements: one member, fp16 output, out_stride == OC, M * OC <= peers->max_n and a multiple of 8, M <= 8
+   * (the weight-streaming kernel); GLOWQ_ERR_UNSUPPORTED_SHAPE otherwise.  NULL = no push.  See glowq_w4a16_peers_t
+   * below for the buffers. */
   const struct glowq_w4a16_peers* push;
   int32_t push_site;
   int32_t reserved2;      /* must be 0 */
@@ -216,16 +218,16 @@ typedef struct glowq_w4a16_peers {
   int32_t world, rank, sites, max_n;
   /* Only for launches that push their result themselves (glowq_w4a16_group_t.push): every rank's second staging
    * buffer of sites * world * max_n 8-byte words, zeroed once and mapped into every rank like `buf`.  A pushed
-   * element travels as ONE 8-byte store {fp16 value, epoch of the call}: the finishing kernel polls each word until
+   * element travels as ONE 8-byte store {fp16 value, epoch of the call}: whoever sums polls each word until
    * it carries the current epoch, so neither fences nor flags are involved.  NULL entries: push is refused. */
   void* ll_buf[GLOWQ_MAX_RANKS];
 } glowq_w4a16_peers_t;
 int glowq_w4a16_allreduce_f16(const glowq_w4a16_peers_t* peers, void* inout, int n, int site, void* stream);
 
-/* Second half of the all-reduce for a launch that pushed its result itself (glowq_w4a16_group_t.push): poll - bounded,
- * status 4 on expiry - every element of every rank's slot of `site` in the local `ll_buf` until it carries the epoch
- * of this rank's latest push on that site, add the `world` values in rank order (fp32) and write the n fp16 sums to
- * `out`.  Every rank calls it after its pushing launch, on the same stream; the sums are bit-identical on all ranks. */
+/* The summing half of a pushed all-reduce as a call of its own: poll - bounded, status 4 on expiry - every element of
+ * every rank's slot of `site` in the local `ll_buf` until it carries the epoch of this rank's latest push on that
+ * site, add the `world` values in rank order (fp32) and write the n fp16 sums to `out`.  A pushing launch does this
+ * itself; the call is for callers that want the sum in a second buffer, and yields the same bits. */
 int glowq_w4a16_allreduce_finish_f16(const glowq_w4a16_peers_t* peers, void* out, int n, int site, void* stream);
 
 /* Bytes of workspace a group call with these sizes needs (sync words + split-K partial sums). */

@@ -29,6 +29,11 @@ SHAPES = {  # name: (output rows of each member, input columns, rank)
     "o13b": ([5120], 5120, 128),
     "qkv14b": ([5120, 1024, 1024], 5120, 256), "o14b": ([5120], 5120, 256), "gu14b": ([17408, 17408], 5120, 256),
     "down14b": ([5120], 17408, 256), "opt_qkv": ([2048, 2048, 2048], 2048, 64),
+    # one rank's shards of the Llama-2-13B layer under 2- and 8-way tensor parallelism
+    "qkv13b_tp2": ([2560, 2560, 2560], 5120, 128), "o13b_tp2": ([5120], 2560, 128),
+    "gu13b_tp2": ([6912, 6912], 5120, 128), "down13b_tp2": ([5120], 6912, 128),
+    "qkv13b_tp8": ([640, 640, 640], 5120, 128), "o13b_tp8": ([5120], 640, 128),
+    "gu13b_tp8": ([1728, 1728], 5120, 128), "down13b_tp8": ([5120], 1792, 128),
 }
 
 

@@ -88,7 +88,11 @@ def _worker(rank, world, port, q):
                     r_buf3 = torch.zeros(M, RANK, dtype=torch.float16, device=dev)
                     y_push = down_sh.launch(h_sh, L=L_down, R=R_down_sh, r_buf=r_buf3, r_mode=K.R_COMPUTE, alpha=1.0,
                                             push=ar, push_site=rep & 1)
+                    # the launch completes the all-reduce itself; the separate finishing call stays valid and
+                    # reproduces the same sum from the same words
+                    y_own = y_push.clone()
                     ar.finish(y_push, site=rep & 1)
+                    assert torch.equal(y_own, y_push), "finishing call changed the sum the launch had written"
                     torch.cuda.synchronize()
                 assert torch.equal(y_push, y), "pushed sum differs from the all-reduce kernel's"
             # gather the sharded h (NCCL, test plumbing only) so that the oracle of down_proj sees the same input
