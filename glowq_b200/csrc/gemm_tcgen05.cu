@@ -1008,9 +1008,9 @@ inline int main_ksplit(int tiles, int nk, int sms) {
 }
 inline int slot_rows_for(int M) { return std::min(BM, ((M + 31) / 32) * 32); }
 inline size_t main_slot_bytes_bound(int M, int IC, int OC_total, int n_members) {
-  // (up to 16 tokens the automatic choice never takes this kernel; a forced call then runs without slicing)
+  // (up to 8 tokens the automatic choice never takes this kernel; a forced call then runs without slicing)
   const int m_tiles = cdiv(M, BM);
-  if (M <= 16 || M > 2 * BM || cdiv(OC_total, 2 * BN) * m_tiles * 2 > kPlanSms) return 0;
+  if (M <= 8 || M > 2 * BM || cdiv(OC_total, 2 * BN) * m_tiles * 2 > kPlanSms) return 0;
   const int tiles_ub = (cdiv(OC_total, BN) + n_members) * m_tiles;  // 128 x 128 tiles
   // at most 8 slices, and slices x (256-column tiles) <= SMs, i.e. at most 2 SMs' worth of 128-column slot tiles
   const int slots_ub = std::min(8 * tiles_ub, 2 * kPlanSms + tiles_ub);
