@@ -178,7 +178,7 @@ def test_abi_exports_every_declared_symbol():
 
 def test_workspace_sizes_cover_what_the_kernels_plan():
     """glowq_w4a16_workspace_bytes is host arithmetic (no GPU): it must grow with what a call may need - R-unit slots
-    with the rank, K-slice slots for 17..256 tokens when the tiles cannot fill the SMs, the sliced last wave above
+    with the rank, K-slice slots for 9..256 tokens when the tiles cannot fill the SMs, the sliced last wave above
     256 tokens - and stay small for decode-sized calls."""
     from glowq_b200.cuda_w4a16 import kernels as K
     ext = K.load_w4a16_extension()
@@ -189,8 +189,11 @@ def test_workspace_sizes_cover_what_the_kernels_plan():
     assert wb(1, 3072, 5120, 0, 3) < wb(1, 3072, 5120, 64, 3) < (1 << 20)
     assert wb(1, 3072, 5120, 64, 3) <= wb(1, 3072, 5120, 256, 3)
     # 17..256 tokens: fp32 partial tiles of the K-sliced GEMM for a launch with few tiles ...
-    small, mid = wb(16, 8192, 3072, 0, 1), wb(32, 8192, 3072, 0, 1)
+    small, mid = wb(8, 8192, 3072, 0, 1), wb(32, 8192, 3072, 0, 1)
     assert mid > small and mid >= 12 * 8 * 2 * 32 * 128 * 4        # 12 tiles x 8 slices x 2 x 32 rows x 128 columns
+    # ... from 9 tokens on, where the automatic choice takes the GEMM (a launch of 9..16 tokens without slot space
+    # would walk all of K in one CTA per tile)
+    assert wb(9, 8192, 3072, 0, 1) == wb(16, 8192, 3072, 0, 1) == mid
     # ... but not for one whose tiles already fill the SMs (2 x 17408 output columns = 136 tiles of 256)
     assert wb(32, 5120, 34816, 0, 2) < (1 << 20)
     # above 256 tokens: room for the sliced last wave (64 slots of a 256 x 256 fp32 tile)
@@ -199,7 +202,7 @@ def test_workspace_sizes_cover_what_the_kernels_plan():
 
 
 def test_workspace_covers_every_k_sliced_plan():
-    """For 17..256 tokens the GEMM may cut K into slices whose fp32 partial tiles live at the end of the workspace; the
+    """For 9..256 tokens the GEMM may cut K into slices whose fp32 partial tiles live at the end of the workspace; the
     size the library reports must cover the plan for either column-tile width (restated here from the host code)."""
     from glowq_b200.cuda_w4a16 import kernels as K
     wb = K.load_w4a16_extension().workspace_bytes
@@ -207,7 +210,7 @@ def test_workspace_covers_every_k_sliced_plan():
     sms = 148
     for ocs in ([3072], [3072, 1024, 1024], [8192, 8192], [5120], [5120, 1024, 1024], [17408, 17408], [384], [136, 200]):
         for ic in (1024, 3072, 8192, 17408):
-            for m in (17, 32, 64, 100, 128, 129, 200, 256):
+            for m in (9, 16, 17, 32, 64, 100, 128, 129, 200, 256):
                 need = 0
                 for nn in (1, 2):
                     tiles = sum(cdiv(oc, 128 * nn) for oc in ocs) * cdiv(m, 128)
