@@ -205,13 +205,18 @@ GemvPlan make_plan(int M, int IC, int n_tiles, int rank, int sms, int split_k) {
   pl.G = ceil_div(IC, kGroup);
   pl.n_tiles = n_tiles;
   const int chunks = ceil_div(pl.G, kChunkGroups);
+  // K is sliced across CTAs on request, when an unsliced CTA does not fit shared memory (long rows with several
+  // tokens: the staged activations and the converted scale pairs grow with the slice length), and for ONE token on
+  // long rows with few tiles (down_proj of the 7B - 14B shapes, K >= 12288): there the slice length is also chosen so
+  // that two CTAs per SM with four ring stages fit.  Measured, microseconds sliced / unsliced: Llama-2-13B down_proj
+  // 19.7 / 20.0, Qwen3-14B 29.6 / 32.5, Qwen2.5-7B 20.0 / 27.2 - but Llama-3.2-3B down_proj (K = 8192) 11.2 / 9.0, and
+  // at two tokens q/k/v of the 13B shape 28.4 / 16.3, its o_proj 15.8 / 9.7, its down_proj 25.3 / 22.2: the combine
+  // of the partial tiles (fence, counter, re-read) costs more than a somewhat shorter K walk saves.
+  const bool slice_long_rows = split_k <= 0 && Mc == 1 && n_tiles < 2 * sms && chunks >= 12;
   int sk = 1;
   if (split_k > 0) {
     sk = std::min(split_k, chunks);
-  } else if (n_tiles < 2 * sms && chunks >= 8) {
-    // Fewer row tiles than resident CTAs AND long rows: slice K too.  Measured on B200: the split-K combine (fence,
-    // counter, re-read of the partial tiles) costs a few microseconds per tile, so it only pays when a CTA would
-    // otherwise stream >= 8 stages alone (down_proj shapes); short rows (o_proj, k/v) are faster unsliced.
+  } else if (slice_long_rows) {
     sk = std::max(1, std::min(ceil_div(2 * sms, std::max(1, n_tiles)), chunks / 4));
   }
   for (;; ++sk) {
@@ -234,12 +239,7 @@ GemvPlan make_plan(int M, int IC, int n_tiles, int rank, int sms, int split_k) {
         }
     }
     if (pl.gps == kChunkGroups) break;  // K cannot be sliced any finer
-    // One or two tokens: two CTAs per SM (16 consumer warps) are worth more than long K slices, so keep slicing while
-    // only one CTA would fit (the per-group shared-memory footprint - staged x, converted scale pairs - grows with
-    // the slice length) or while the ring would be shallower than four stages (measured on the Llama-2-13B down_proj:
-    // three slices of 40 groups with four stages beat two slices of 56 groups with three, 16.2 vs 17.6 us).  More
-    // tokens stage too much x for that; they take what fits.
-    const bool want_two = split_k <= 0 && Mc <= 2 && sk < 8 && n_tiles * (sk + 1) <= 8 * sms;
+    const bool want_two = slice_long_rows && sk < 8 && n_tiles * (sk + 1) <= 8 * sms;
     if (pl.stages > 0 && ((pl.ctas_per_sm == 2 && pl.stages >= 4) || !want_two)) break;
   }
   if (forced_stages > 0 && pl.stages > 0) pl.stages = std::max(2, std::min(forced_stages, pl.stages));
