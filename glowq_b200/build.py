@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libglowq_w4a16.so")
-SOURCES = ["abi.cu", "gemv_stream.cu", "dequant.cu", "gemm_tcgen05.cu", "tp_allreduce.cu"]
+SOURCES = ["abi.cu", "gemv_stream.cu", "dequant.cu", "gemm_tcgen05.cu", "tp_allreduce.cu", "r_product.cu"]
 HEADERS = ["common.cuh", "params.h", os.path.join("..", "..", "include", "glowq_w4a16.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]

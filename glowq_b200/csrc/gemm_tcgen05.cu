@@ -32,12 +32,14 @@
 
 namespace glowq {
 
-// r = x . R^T for up to 16 tokens by the streaming kernel's R units (gemv_stream.cu).  Measured on the Llama-2-13B
-// shapes (group call, microseconds, this path / the K-sliced GEMM + slot sum): q/k/v 39.8 / 44.1 at 16 tokens,
-// 43.6 / 45.0 at 32, 54.9 / 47.8 at 64 - the token blocks of a unit are worked through one after the other.
-constexpr int kRSmallMaxM = 16;
-size_t r_small_slot_bytes(int M, int IC, int rank);
-cudaError_t launch_r_small(const GemvParams& p, cudaStream_t stream);
+// r = x . R^T for up to 128 tokens as one small launch (r_product.cu); above, the K-sliced GEMM of this file.  Measured
+// group calls (microseconds, this path / GEMM + slot sum): Llama-2-13B q/k/v 40.2 / 45.1 at 32 tokens, 51.8 / 56.6 at
+// 128, 68.4 / 70.8 at 256; Qwen3-14B down_proj (rank 256, K = 17408) 63.8 / 62.5 at 128 but 111.7 / 96.4 at 256, where
+// every 64-token block stages the R tiles again.
+constexpr int kRProductMaxM = 128;
+size_t r_product_slot_bytes(int M, int IC, int rank);
+cudaError_t launch_r_product(const __half* x, const __half* R, __half* r_buf, float* slots, uint32_t* ctr, int M, int IC,
+                             int rank, int x_stride, int R_stride, cudaStream_t stream);
 int tensor_map_2d_ex(CUtensorMap* out, CUtensorMapDataType dtype, const void* ptr, uint64_t dim0, uint64_t dim1,
                      uint64_t stride_bytes, uint32_t box0, uint32_t box1, int swizzle128);
 
@@ -1025,7 +1027,7 @@ inline size_t main_slot_bytes_bound(int M, int IC, int OC_total, int n_members) 
 
 size_t gemm_workspace_bytes(int M, int IC, int OC_total, int rank, int n_members) {
   size_t slots = std::max(rank > 0 ? r_slot_bytes(M, IC, rank) : 0, main_slot_bytes_bound(M, IC, OC_total, n_members));
-  if (rank > 0 && M <= kRSmallMaxM) slots = std::max(slots, r_small_slot_bytes(M, IC, rank));
+  if (rank > 0 && M <= kRProductMaxM) slots = std::max(slots, r_product_slot_bytes(M, IC, rank));
   if (M > 2 * BM) slots = std::max(slots, static_cast<size_t>(kMaxTailSlots) * 2 * 2 * BM * BN * 4);  // sliced last wave
   if (slots == 0) return kWsHeaderBytes;
   return counters_end(OC_total, n_members) + slots + 256;
@@ -1048,34 +1050,20 @@ int gemm_group_forward(const glowq_w4a16_group_t& g, cudaStream_t stream, cudaEr
   if ((rc = map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.x, g.IC, g.M, static_cast<uint64_t>(g.x_stride) * 2, BK, BM, 1)))
     return rc;
 
-  // r = X . R^T, once per group, into r_buf.  Up to 16 tokens: the R units of the weight-streaming kernel as a launch
-  // of their own (the K-sliced GEMM below plus its slot sum take about twenty microseconds).
+  // r = X . R^T, once per group, into r_buf.  Up to 128 tokens: one small launch (r_product.cu); the K-sliced GEMM
+  // below plus its slot sum take about twenty microseconds.
   bool r_done = false;
-  if (g.r_mode == GLOWQ_R_COMPUTE && g.M <= kRSmallMaxM) {
+  if (g.r_mode == GLOWQ_R_COMPUTE && g.M <= kRProductMaxM && cdiv(g.rank, 16) * cdiv(g.M, 64) <= kRpCtrWords) {
     int oc_total = 0;
     for (int i = 0; i < g.n_members; ++i) oc_total += g.members[i].OC;
-    const size_t need = r_small_slot_bytes(g.M, g.IC, g.rank);
+    const size_t need = r_product_slot_bytes(g.M, g.IC, g.rank);
     const size_t off = g.workspace_bytes >= need ? ((g.workspace_bytes - need) & ~static_cast<size_t>(255)) : 0;
     if (off >= counters_end(oc_total, g.n_members)) {
-      GemvParams rp{};
-      rp.x = static_cast<const __half*>(g.x);
-      rp.R = static_cast<const __half*>(g.R);
-      rp.r_buf = static_cast<__half*>(g.r_buf);
-      rp.ws_head = static_cast<uint32_t*>(g.workspace);
-      rp.r_partial = reinterpret_cast<float*>(static_cast<unsigned char*>(g.workspace) + off);
-      rp.M = g.M;
-      rp.IC = g.IC;
-      rp.x_stride = g.x_stride;
-      rp.R_stride = g.R_stride;
-      rp.G = G;
-      rp.rank = g.rank;
-      rp.r_mode = GLOWQ_R_COMPUTE;
-      rp.n_r_tiles = cdiv(g.rank, kRTileRows);
-      rp.gpr = cdiv(G, cdiv(G, kChunkGroups));
-      rp.SKr = cdiv(G, rp.gpr);
-      rp.n_r_units = rp.n_r_tiles * rp.SKr;
-      rp.x_vec_ok = 1;   // gemm_supported: x is 16-byte aligned with a stride that is a multiple of 8
-      const cudaError_t e = launch_r_small(rp, stream);
+      unsigned char* ws = static_cast<unsigned char*>(g.workspace);
+      const cudaError_t e = launch_r_product(static_cast<const __half*>(g.x), static_cast<const __half*>(g.R),
+                                             static_cast<__half*>(g.r_buf), reinterpret_cast<float*>(ws + off),
+                                             reinterpret_cast<uint32_t*>(ws + kWsHeaderBytes), g.M, g.IC, g.rank, g.x_stride,
+                                             g.R_stride, stream);
       if (e != cudaSuccess) {
         *cuda_err = e;
         return GLOWQ_ERR_CUDA;

@@ -362,8 +362,7 @@ __device__ __forceinline__ uint32_t launch_epoch(uint32_t eword) {
 // flag and no fence on the reading side, and every reader sees the same bits.
 template <int NT>
 __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride, float* red, float* fin,
-                                        bool& dep_wait_pending, uint32_t& eword, const float* s_rstd, bool do_norm,
-                                        bool standalone = false) {
+                                        bool& dep_wait_pending, uint32_t& eword, const float* s_rstd, bool do_norm) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   if (u0 >= p.n_r_units) return;
   uint4 a[4], b[4];
@@ -405,7 +404,7 @@ __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride
     for (int gl = warp; gl < ng || gl == warp; gl += kConsumerWarps) {
       const bool more_rounds = gl + kConsumerWarps < ng;
       if (gl != warp || unit != u0) load_round(unit, gl, true);
-      dep_wait(p, dep_wait_pending, eword, !standalone);  // R is static, x is not: the earlier kernels must be complete before x is read
+      dep_wait(p, dep_wait_pending, eword, true);  // R is static, x is not: the earlier kernels must be complete before x is read
       if (gl < ng) {
         const int kb = (gbase + gl) * kGroup + 32 * t;
 #pragma unroll
@@ -448,7 +447,7 @@ __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride
     for (int e = threadIdx.x; e < NT * 128; e += kConsumerThreads) slot[e] = fin[e];
     ++n_done;
   }
-  dep_wait(p, dep_wait_pending, eword, !standalone);
+  dep_wait(p, dep_wait_pending, eword, true);
   consumer_sync();
   uint32_t* last_flag = reinterpret_cast<uint32_t*>(fin);   // fin is free again
   if (threadIdx.x == 0) {
@@ -462,8 +461,7 @@ __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride
   }
   consumer_sync();
   if (*last_flag != 0u) {
-    // (a launch that only computes r has no row tiles that poll the words: it writes r_buf alone)
-    const uint32_t epoch = standalone ? 0u : launch_epoch(eword);
+    const uint32_t epoch = launch_epoch(eword);
     const int q4 = p.rank >> 2;  // rank is a multiple of 8
     for (int i = threadIdx.x; i < p.M * q4; i += kConsumerThreads) {
       const int tok = i / q4, j = (i - tok * q4) * 4;
@@ -482,18 +480,15 @@ __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride
       }
       const __half2 h01 = __floats2half2_rn(s.x, s.y), h23 = __floats2half2_rn(s.z, s.w);
       const uint32_t u01 = *reinterpret_cast<const uint32_t*>(&h01), u23 = *reinterpret_cast<const uint32_t*>(&h23);
-      if (!standalone) {
-        uint2* w = p.r_ll + static_cast<size_t>(tok) * (p.rank >> 1) + (j >> 1);
-        w[0] = make_uint2(u01, epoch);
-        w[1] = make_uint2(u23, epoch);
-      }
+      uint2* w = p.r_ll + static_cast<size_t>(tok) * (p.rank >> 1) + (j >> 1);
+      w[0] = make_uint2(u01, epoch);
+      w[1] = make_uint2(u23, epoch);
       if (p.r_buf != nullptr) *reinterpret_cast<uint2*>(p.r_buf + static_cast<size_t>(tok) * p.rank + j) = make_uint2(u01, u23);
     }
     // Nothing of this launch touches the unit counter any more; the epoch moves on once every consumer warp of the
     // grid has taken it (all CTAs are resident and register right after the wait for the previous kernels, so this
     // is normally true long before r is complete).  Off the path of r: the words above are already on their way.
-    if (threadIdx.x == 0 && standalone) p.ws_head[WS_R_DONE] = 0u;
-    if (threadIdx.x == 0 && !standalone) {
+    if (threadIdx.x == 0) {
       p.ws_head[WS_R_DONE] = 0u;
       const uint32_t readers = static_cast<uint32_t>(kConsumerWarps) * gridDim.x;
       uint32_t spins = 0;
@@ -1209,23 +1204,6 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   }
 }
 
-// r = x . R^T alone, for launches of 9 to 16 tokens (instantiated up to 64) whose linears run on the tensor-core GEMM: the R units of the
-// streaming kernel, one per CTA, with NT blocks of 8 tokens on the MMA N axis.  The CTA that completes the count adds the
-// K-slice slots in slot order and writes r_buf (fp16).  One launch of a few microseconds instead of a K-sliced GEMM
-// and a slot sum.
-template <int NT>
-__global__ void __launch_bounds__(kConsumerThreads) r_small_kernel(const __grid_constant__ GemvParams p) {
-  extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ float s_rstd[8];
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  float* red = reinterpret_cast<float*>(smem);
-  float* fin = red + kConsumerWarps * NT * 128;
-  bool dep_wait_pending = true;
-  uint32_t eword = 0u;
-  r_units<NT>(p, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), red, fin, dep_wait_pending, eword, s_rstd, false,
-              true);
-}
-
 // Any-shape scalar kernel for layouts the streaming kernel does not take (group_size != 128, packed
 // rows that are not 16-byte aligned).  One warp per output row; fp32 accumulation.
 __global__ void __launch_bounds__(256) w4a16_generic_kernel(const __half* x, const int32_t* qweight, const __half* scales,
@@ -1335,44 +1313,6 @@ cudaError_t launch_gemv_stream(const GemvParams& p, const TensorMaps& tm, int NT
     case kFeatSliced | kFeatCorr: return launch_feat<kFeatSliced | kFeatCorr>(p, tm, grid, stream);
     case kFeatSliced | kFeatExtras: return launch_feat<kFeatSliced | kFeatExtras>(p, tm, grid, stream);
     default: return launch_feat<kFeatSliced | kFeatCorr | kFeatExtras>(p, tm, grid, stream);
-  }
-}
-
-// Workspace bytes of the slots r_small_kernel needs, and its launch (M <= 64; p.r_partial, p.ws_head, p.r_buf set).
-// The caller decides up to how many tokens it pays.
-size_t r_small_slot_bytes(int M, int IC, int rank) {
-  const int NT = (M + 7) / 8, G = (IC + kGroup - 1) / kGroup, chunks = (G + kChunkGroups - 1) / kChunkGroups;
-  return static_cast<size_t>((rank + kRTileRows - 1) / kRTileRows) * chunks * NT * 128 * 4;
-}
-cudaError_t launch_r_small(const GemvParams& p, cudaStream_t stream) {
-  const int NT = (p.M + 7) / 8;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(p.n_r_units);
-  cfg.blockDim = dim3(kConsumerThreads);
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  static const bool use_pdl = [] {
-    const char* v = std::getenv("GLOWQ_PDL");
-    return !(v && v[0] == '0');
-  }();
-  cfg.numAttrs = use_pdl ? 1 : 0;
-  auto go = [&](auto kernel, int nt) {
-    cfg.dynamicSmemBytes = static_cast<size_t>(kConsumerWarps * nt * 128 + nt * 128) * 4;
-    return cudaLaunchKernelEx(&cfg, kernel, p);
-  };
-  switch (NT) {
-    case 1: return go(r_small_kernel<1>, 1);
-    case 2: return go(r_small_kernel<2>, 2);
-    case 3: return go(r_small_kernel<3>, 3);
-    case 4: return go(r_small_kernel<4>, 4);
-    case 5: return go(r_small_kernel<5>, 5);
-    case 6: return go(r_small_kernel<6>, 6);
-    case 7: return go(r_small_kernel<7>, 7);
-    case 8: return go(r_small_kernel<8>, 8);
-    default: return cudaErrorInvalidValue;
   }
 }
 

@@ -49,10 +49,11 @@ constexpr uint32_t kEpochReaderMask = (1u << kEpochShift) - 1u;
 constexpr uint32_t kEpochMask = (1u << 20) - 1u;
 constexpr size_t kWsHeaderBytes = WS_HEADER_WORDS * 4;
 constexpr int kMaxRTiles = 64;      // rank <= 1024
-// After the header: 256 B of per-R-tile words, then r of the running launch as the row tiles read it - 8-byte words
+// After the header: 1 KB of arrival counters for the stand-alone r product, then r of the running launch as the row tiles read it - 8-byte words
 // {half2(r[tok][2j], r[tok][2j+1]), launch epoch}, up to 8 tokens x rank 1024 - then the tile counters.  Launches of
 // the other kernels keep clear of everything up to the end of the tile counters.
-constexpr size_t kWsRllOffset = kWsHeaderBytes + kMaxRTiles * 4;
+constexpr int kRpCtrWords = 256;    // arrival counters of the stand-alone r product (rank / 16 x token blocks of 64)
+constexpr size_t kWsRllOffset = kWsHeaderBytes + kRpCtrWords * 4;
 constexpr size_t kWsRllBytes = 8 * 1024 * 4;
 constexpr size_t kWsTileCtrOffset = kWsRllOffset + kWsRllBytes;
 constexpr int kMaxPrefetch = kMaxMembers + 1;
