@@ -433,7 +433,7 @@ int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cuda
     if (fast) {
       if (pl.stages < 2 || gemv_smem_bytes(p, pl.NT) > kSmemOnePerSm) return GLOWQ_ERR_UNSUPPORTED_SHAPE;
       // persistent grid: every CTA resident at once, a whole number of CTAs per K slice
-      // R units run on dedicated CTAs at the end of the grid (several units each when there are many), so that the
+      // R units run on dedicated CTAs (the lowest block indices; several units each when there are many), so that the
       // r chain (R loads, MMAs, slot, release counter) overlaps the other CTAs' x staging and weight streaming
       static const int max_r_ctas = env_int("GLOWQ_GEMV_R_CTAS", 96);
       // (the epoch word of the workspace counts the consumer warps of a grid in kEpochShift bits)

@@ -18,14 +18,20 @@
 //     weights once).  Each group's fp32 result takes two FMAs with the converted pair: the scale, and the zero-point
 //     as -z * scale * sum(x over the group).
 //   * Optionally the activations are transformed while they are staged: residual add and RMSNorm.
-//   * r = R_g . x is produced inside the launch by "R units" (16 rows of R x a K slice) run by extra CTAs at the end
-//     of the grid (and, with K slices, by the CTAs of slices that apply no correction); each unit stores an fp32 slot,
-//     a CTA publishes its units with one add to a release counter, and whoever needs r adds the slots of an R tile in
-//     slot order (identical bits everywhere) and rounds to fp16.  The grid never exceeds what is resident at once, so
-//     the bounded wait before the first L_i epilogue never depends on an unscheduled CTA.
+//   * r = R_g . x is produced inside the launch by "R units" (16 rows of R x a K slice) run by extra CTAs (the lowest
+//     block indices, placed first; with K slices also by the CTAs of slices that apply no correction).  Each unit
+//     stores an fp32 slot, a CTA publishes its units with one add to a release counter, and the CTA that completes
+//     the count adds the slots in slot order, rounds to fp16 and writes r to r_buf and - as 8-byte words {two
+//     elements, launch epoch} - to the workspace, where the row tiles poll the words they need (one L2 round trip, no
+//     flag; identical bits everywhere).  The grid never exceeds what is resident at once, so the bounded poll before
+//     the first L_i epilogue never depends on an unscheduled CTA.
 //   * K can be sliced across CTAs; the last CTA to arrive at a tile sums the slices in slice order.
-//   * Tensor-parallel row-split launches may store their result to every rank's staging slot themselves, as 8-byte
-//     words {fp16 value, call epoch}; a small finishing kernel polls the words and adds them in rank order.
+//   * Tensor-parallel row-split launches may perform their all-reduce themselves: tiles store their result to every
+//     rank's word buffer as 8-byte words {fp16 value, call epoch}, and the launch's last CTAs poll all ranks' words in
+//     the local buffer, add them in rank order and write the output.
+//   * The weight stages land swizzled (128-byte pattern of the tensor map) so that the consumers' 128-bit loads are
+//     free of bank conflicts, and the kernel is instantiated per feature set (correction, extras) so that launches
+//     do not carry the code of features they do not use.
 // Every wait (mbarrier, release counter) is bounded; on expiry the kernel records a status word and drains.
 #include <cstdlib>
 

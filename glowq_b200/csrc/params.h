@@ -93,7 +93,7 @@ struct GemvParams {
   int n_tiles, SK, gps;          // main work: tiles x K slices, groups per slice (multiple of kChunkGroups)
   int n_r_tiles, SKr, gpr;       // r work: 16-row tiles of R x SKr K slices of gpr groups each
   int n_r_units;                 // n_r_tiles * SKr (0 unless r_mode == COMPUTE)
-  int n_r_ctas;                  // CTAs at the end of the grid that only run R units
+  int n_r_ctas;                  // CTAs (the lowest block indices) that run the R units before any row tile
   int x_vec_ok;                  // x rows are 16-byte aligned
   int xs_stride;                 // bytes between tokens of the staged x slice in shared memory
   int stages;                    // weight ring depth
