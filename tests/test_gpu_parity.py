@@ -243,6 +243,30 @@ def test_fused_residual_rmsnorm_prologue(ocs, ic, rank, M, with_res):
     assert ext().lib.glowq_w4a16_group_forward(g) == 1          # residual / hidden_out without a norm weight
 
 
+
+@pytest.mark.parametrize("M,ic,rank", [(9, 1152, 8), (16, 2048, 64), (40, 3200, 24), (64, 1024, 136), (65, 2176, 64),
+                                       (128, 5120, 128), (129, 2048, 64)])
+def test_r_for_few_tokens_and_the_group_gemm(M, ic, rank):
+    """9..128 tokens take the tensor-core GEMM, with r = x R^T from the small stand-alone launch (one CTA per 16 rows
+    of R x 1024 columns x 64 tokens, K slices added in order by the last CTA to arrive); 129 tokens take the K-sliced
+    GEMM for r.  Ranks that are not multiples of 16, K that is not a multiple of 1024, token counts that do not fill
+    the 64-token blocks; run twice on the same workspace (the arrival counters must be back at zero)."""
+    rng = np.random.default_rng(40 + M)
+    lins = [Linear(rng, oc, ic, rank=rank) for oc in (384, 200)]
+    R = (np.random.default_rng(41).standard_normal((rank, ic)) * 0.01).astype(np.float16)
+    x = np.random.default_rng(42).standard_normal((M, ic)).astype(np.float16)
+    x_d, R_d = dev(x), dev(R)
+    r_want = x.astype(np.float32) @ R.astype(np.float32).T
+    g = None
+    for rep in range(2):
+        r_buf = torch.zeros(M, rank, dtype=torch.float16, device="cuda")
+        outs = [new_out(M, l) for l in lins]
+        g = make_group(x_d, lins, outs, R_d=R_d, r_buf=r_buf, r_mode=K.R_COMPUTE, ws=None if g is None else g._keep[-1])
+        assert run_group(g) == 0 and status_ok(g) == 0
+        assert np.abs(r_buf.float().cpu().numpy() - r_want).max() <= 2e-3, f"r, pass {rep}"
+        for i, (l, o) in enumerate(zip(lins, outs)):
+            assert_close(o, l.oracle(x, R), tag=f"member {i}, pass {rep}")
+
 # ---------------------------------------------------------------------------------------------- tensor-core GEMM
 @pytest.mark.parametrize("M,oc,ic,rank,alpha,bias", [
     (64, 256, 512, 0, 1.0, False), (128, 128, 128, 0, 1.0, False), (200, 136, 1152, 0, 1.0, True),
