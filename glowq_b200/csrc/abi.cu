@@ -469,8 +469,11 @@ int gemv_group_forward(const glowq_w4a16_group_t& g, const DeviceInfo& dev, cuda
       }
       // L2 prefetch requests for the call that follows on this stream: its right factor, then a prefix of its packed
       // rows in tile order (what its CTAs read first)
-      static const int pf_mb = env_int("GLOWQ_GEMV_PREFETCH_MB", 32);
-      static const int deep_pf = env_int("GLOWQ_GEMV_DEEP_PREFETCH", 1);
+      // Defaults from the Llama-2-13B token step (ms, next-call megabytes / in-launch lookahead): 16/off 2.365,
+      // 8/off 2.357, 16/on 2.369, 32/on 2.440, 64/on 2.590, 0/off 2.407 - more than the head of the next call evicts
+      // what this one still needs, and the lookahead no longer pays on top of it.
+      static const int pf_mb = env_int("GLOWQ_GEMV_PREFETCH_MB", 16);
+      static const int deep_pf = env_int("GLOWQ_GEMV_DEEP_PREFETCH", 0);
       p.deep_prefetch = deep_pf;
       p.n_pf = 0;
       if (g.next != nullptr && pf_mb > 0 && m0 + kGemvMaxM >= g.M) {
