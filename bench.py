@@ -23,7 +23,7 @@ sys.path.insert(0, ROOT)
 
 # mean DRAM bytes (read + write) per gemv_stream_kernel launch of a batch-1 token step, from ncu captures of this
 # bench command (profiles/gemv_stream_*_decode_launches.md), keyed by (model, batch)
-NCU_DRAM_BYTES_PER_LAUNCH = {("llama-3.2-3b", 1): 14.38e6, ("llama-2-13b", 1): 46.62e6}
+NCU_DRAM_BYTES_PER_LAUNCH = {("llama-3.2-3b", 1): 14.38e6, ("llama-2-13b", 1): 46.58e6}
 
 # decode-sized vectors go through the one-CTA peer-store all-reduce; anything larger (prefill) through NCCL
 PEER_AR_MAX_ELEMS = 64 * 1024
