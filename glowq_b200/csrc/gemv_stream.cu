@@ -343,18 +343,16 @@ __device__ __forceinline__ void cross_warp_reduce(float (&acc)[NB][4], float* re
   consumer_sync();
 }
 
-// The wait for the previous kernels of the stream, once per consumer warp.  In a correcting launch lane 0 then
-// registers the warp as a reader of the workspace's epoch word; the value the add returns (kept in lane 0 until the
-// epoch is needed, so that nobody waits for the round trip here) carries the epoch of the PREVIOUS correcting launch.
-__device__ __forceinline__ void dep_wait(const GemvParams& p, bool& pending, uint32_t& eword, bool computes_r) {
+// The wait for the previous kernels of the stream, once per warp.
+__device__ __forceinline__ void dep_wait(bool& pending) {
   if (!pending) return;
   asm volatile("griddepcontrol.wait;" ::: "memory");
   pending = false;
-  if (computes_r && (threadIdx.x & 31) == 0) eword = atomicAdd(p.ws_head + WS_EPOCH, 1u);
 }
-// Epoch that stamps the words of r in this launch (never 0, the value of a word that was never written).
+// Epoch that stamps the words of r in this launch (never 0, the value of a word that was never written), from the
+// epoch word as the CTA's registration found it: it carries the epoch of the PREVIOUS correcting launch.
 __device__ __forceinline__ uint32_t launch_epoch(uint32_t eword) {
-  const uint32_t e = ((__shfl_sync(0xffffffffu, eword, 0) >> kEpochShift) + 1u) & kEpochMask;
+  const uint32_t e = ((eword >> kEpochShift) + 1u) & kEpochMask;
   return e == 0u ? 1u : e;
 }
 
@@ -368,7 +366,8 @@ __device__ __forceinline__ uint32_t launch_epoch(uint32_t eword) {
 // flag and no fence on the reading side, and every reader sees the same bits.
 template <int NT>
 __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride, float* red, float* fin,
-                                        bool& dep_wait_pending, uint32_t& eword, const float* s_rstd, bool do_norm) {
+                                        bool& dep_wait_pending, const volatile uint32_t* s_eword, uint32_t epoch_bar_u32,
+                                        Ctx cx, const float* s_rstd, bool do_norm) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   if (u0 >= p.n_r_units) return;
   uint4 a[4], b[4];
@@ -410,7 +409,7 @@ __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride
     for (int gl = warp; gl < ng || gl == warp; gl += kConsumerWarps) {
       const bool more_rounds = gl + kConsumerWarps < ng;
       if (gl != warp || unit != u0) load_round(unit, gl, true);
-      dep_wait(p, dep_wait_pending, eword, true);  // R is static, x is not: the earlier kernels must be complete before x is read
+      dep_wait(dep_wait_pending);  // R is static, x is not: the earlier kernels must be complete before x is read
       if (gl < ng) {
         const int kb = (gbase + gl) * kGroup + 32 * t;
 #pragma unroll
@@ -453,7 +452,7 @@ __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride
     for (int e = threadIdx.x; e < NT * 128; e += kConsumerThreads) slot[e] = fin[e];
     ++n_done;
   }
-  dep_wait(p, dep_wait_pending, eword, true);
+  dep_wait(dep_wait_pending);
   consumer_sync();
   uint32_t* last_flag = reinterpret_cast<uint32_t*>(fin);   // fin is free again
   if (threadIdx.x == 0) {
@@ -467,7 +466,8 @@ __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride
   }
   consumer_sync();
   if (*last_flag != 0u) {
-    const uint32_t epoch = launch_epoch(eword);
+    mbar_wait_u32(epoch_bar_u32, 0, cx);   // the CTA's registration (its aux warp) has returned
+    const uint32_t epoch = launch_epoch(*s_eword);
     const int q4 = p.rank >> 2;  // rank is a multiple of 8
     for (int i = threadIdx.x; i < p.M * q4; i += kConsumerThreads) {
       const int tok = i / q4, j = (i - tok * q4) * 4;
@@ -496,7 +496,7 @@ __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride
     // is normally true long before r is complete).  Off the path of r: the words above are already on their way.
     if (threadIdx.x == 0) {
       p.ws_head[WS_R_DONE] = 0u;
-      const uint32_t readers = static_cast<uint32_t>(kConsumerWarps) * gridDim.x;
+      const uint32_t readers = gridDim.x;   // one registration per CTA
       uint32_t spins = 0;
       bool all_in = true;
       while ((ld_acquire_u32(p.ws_head + WS_EPOCH) & kEpochReaderMask) != readers) {
@@ -561,6 +561,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   const __half* const norm_w = (FEAT & kFeatExtras) ? p.norm_w : nullptr;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_abort;
+  __shared__ uint32_t s_eword;   // the workspace's epoch word as this CTA's registration found it
   __shared__ float s_rstd[8];   // fused RMSNorm: 1 / rms of every token row
   constexpr int RT = kRowTiles;
   constexpr int NB = RT * NT;  // 16-row x 8-token fragment blocks per tile
@@ -572,6 +573,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   uint64_t* cooked_full = meta_full + kMetaDepth;     // [kCookedDepth]: a tile's converted pairs are written
   uint64_t* cooked_empty = cooked_full + kCookedDepth;  // ... and the consumer warps are done with them
   uint64_t* red_empty = cooked_empty + kCookedDepth;  // the aux warp has drained the reduction buffer
+  uint64_t* epoch_bar = red_empty + 1;                // the CTA's registration on the workspace's epoch word has returned
   // the swizzle of the weight stages works on shared-memory address bits: stages start on 1024-byte boundaries
   unsigned char* ring = smem + 256 + ((1024u - ((smem_u32(smem) + 256u) & 1023u)) & 1023u);
   const int meta_bytes = kTileRows * (p.meta_gp * 2 + p.meta_gw * 4);
@@ -634,6 +636,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       mbar_init(cooked_empty + i, kConsumerWarps);
     }
     mbar_init(red_empty, 1);
+    mbar_init(epoch_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (threadIdx.x >= 32 && threadIdx.x < 32 + kZeroRowBytes / 4) reinterpret_cast<uint32_t*>(zero_row)[threadIdx.x - 32] = 0u;
@@ -644,6 +647,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   const uint32_t mfull_u32 = smem_u32(meta_full);
   const uint32_t cfull_u32 = smem_u32(cooked_full), cempty_u32 = smem_u32(cooked_empty);
   const uint32_t rempty_u32 = smem_u32(red_empty);
+  const uint32_t epoch_bar_u32 = smem_u32(epoch_bar);
 
   if (warp == kConsumerWarps) {
     // ================================================================ weight / L copy warp
@@ -793,6 +797,18 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     };
     while (k_m < kMetaDepth && tile_at(k_m) < p.n_tiles) prefetch_raw();
     if (tile_at(0) < p.n_tiles) cook(0);
+    // A correcting launch: ONE add per CTA registers it as a reader of the workspace's epoch word, once the previous
+    // kernels are complete (eight adds per CTA - one per consumer warp - were 2400 operations on one address right
+    // when every CTA comes out of its wait, and staggered the CTAs by a microsecond).  The consumers pick the value
+    // up behind a barrier, at their first L epilogue.
+    bool aux_dep_pending = true;
+    if (r_mode == 1) {
+      dep_wait(aux_dep_pending);
+      if (lane == 0) {
+        s_eword = atomicAdd(p.ws_head + WS_EPOCH, 1u);
+        mbar_arrive(epoch_bar);
+      }
+    }
     for (int k = 0, tile; (tile = tile_at(k)) < p.n_tiles; ++k) {
       // raw slot k % kMetaDepth was cooked in the previous round: refill it with the tile three ahead
       if (k_m == k + kMetaDepth && tile_at(k_m) < p.n_tiles) prefetch_raw();
@@ -802,7 +818,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
 
       // ---- epilogue of `tile` (outputs may still be read by the previous kernel until it has completed)
       if (k == 0) {
-        asm volatile("griddepcontrol.wait;" ::: "memory");
+        dep_wait(aux_dep_pending);
         if (push_world > 0) push_e = *p.push_epoch + 1u;
       }
       const TileInfo ti = tile_info(p, tile, slice, r_mode);
@@ -893,7 +909,6 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
     // ================================================================ consumer warps
     const int g = lane >> 2, t = lane & 3;
     bool dep_wait_pending = true;  // x (and a loaded r) come from earlier kernels of the stream
-    uint32_t eword = 0u;           // lane 0: the epoch word as this warp's registration found it
     uint32_t r_epoch = 0u;         // epoch of the words that carry r of this launch (set at the first L epilogue)
     {
       // Launch parameters live in constant memory, and the first touch of each of their cache lines is a miss of a few
@@ -907,7 +922,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
                    "r"(SK), "r"(p.out_fp32), "r"(push_world), "l"(norm_w));
     }
     if (norm_w != nullptr) {     // the row statistics come first: both the R units and the staging need them
-      dep_wait(p, dep_wait_pending, eword, r_mode == 1);
+      dep_wait(dep_wait_pending);
       norm_stats(p, red, s_rstd);
     }
     // R units of this CTA (first unit, stride; none if ru0 < 0).  The grid is persistent - never larger than what is
@@ -929,9 +944,9 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       rstride = static_cast<int>(gridDim.x);
     }
     if (r_mode == 1 && ru0 >= 0)
-      r_units<NT>(p, ru0, rstride, red, fin, dep_wait_pending, eword, s_rstd, norm_w != nullptr);
+      r_units<NT>(p, ru0, rstride, red, fin, dep_wait_pending, &s_eword, epoch_bar_u32, cx, s_rstd, norm_w != nullptr);
     if (threadIdx.x == 0 && r_only) trace_event(p, 6);
-    dep_wait(p, dep_wait_pending, eword, r_mode == 1);
+    dep_wait(dep_wait_pending);
     if (push_world > 0) push_e = *p.push_epoch + 1u;
     if (threadIdx.x == 0) trace_event(p, 2);
     // per warp: no CTA-wide barrier needed.  A CTA without row tiles (an R CTA of a launch with few tiles) stages
@@ -1052,7 +1067,10 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
         float al[NB][4];
 #pragma unroll
         for (int b = 0; b < NB; ++b) al[b][0] = al[b][1] = al[b][2] = al[b][3] = 0.f;
-        if (!r_ready && r_mode == 1) r_epoch = launch_epoch(eword);   // the registration's round trip is long over
+        if (!r_ready && r_mode == 1) {   // the registration's round trip is long over
+          ok = ok && mbar_wait_u32(epoch_bar_u32, 0, cx);
+          r_epoch = launch_epoch(*static_cast<volatile uint32_t*>(&s_eword));
+        }
         for (int l = 0; l < n_lstages; ++l) {
           ok = ok && mbar_wait_u32(full_u32 + st * 8, ph, cx);
           if (threadIdx.x == 0 && k == 0 && l == 0) trace_event(p, 11);
