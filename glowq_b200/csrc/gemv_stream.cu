@@ -367,7 +367,7 @@ __device__ __forceinline__ uint32_t launch_epoch(uint32_t eword) {
 template <int NT>
 __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride, float* red, float* fin,
                                         bool& dep_wait_pending, const volatile uint32_t* s_eword, uint32_t epoch_bar_u32,
-                                        Ctx cx, const float* s_rstd, bool do_norm) {
+                                        Ctx cx, const float* s_rstd, bool do_norm, bool& closes_epoch) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   if (u0 >= p.n_r_units) return;
   uint4 a[4], b[4];
@@ -491,25 +491,25 @@ __device__ __forceinline__ void r_units(const GemvParams& p, int u0, int ustride
       w[1] = make_uint2(u23, epoch);
       if (p.r_buf != nullptr) *reinterpret_cast<uint2*>(p.r_buf + static_cast<size_t>(tok) * p.rank + j) = make_uint2(u01, u23);
     }
-    // Nothing of this launch touches the unit counter any more; the epoch moves on once every consumer warp of the
-    // grid has taken it (all CTAs are resident and register right after the wait for the previous kernels, so this
-    // is normally true long before r is complete).  Off the path of r: the words above are already on their way.
-    if (threadIdx.x == 0) {
-      p.ws_head[WS_R_DONE] = 0u;
-      const uint32_t readers = gridDim.x;   // one registration per CTA
-      uint32_t spins = 0;
-      bool all_in = true;
-      while ((ld_acquire_u32(p.ws_head + WS_EPOCH) & kEpochReaderMask) != readers) {
-        __nanosleep(128);
-        if (++spins > kSpinLimit) {
-          atomicExch(p.ws_head + WS_STATUS, 1u);
-          all_in = false;
-          break;
-        }
-      }
-      if (all_in) p.ws_head[WS_EPOCH] = epoch << kEpochShift;
+    if (threadIdx.x == 0) p.ws_head[WS_R_DONE] = 0u;   // nothing of this launch touches the unit counter any more
+    closes_epoch = true;   // (the caller advances the epoch when the CTA retires: see advance_epoch)
+  }
+}
+
+// The epoch of the workspace moves on once every CTA of the grid has registered on it.  All CTAs are resident and
+// register right after the wait for the previous kernels; the CTA that completed r does this as its last action, long
+// after, so the loop normally ends at once (bounded all the same).
+__device__ __forceinline__ void advance_epoch(const GemvParams& p, uint32_t eword) {
+  const uint32_t readers = gridDim.x;   // one registration per CTA
+  uint32_t spins = 0;
+  while ((ld_acquire_u32(p.ws_head + WS_EPOCH) & kEpochReaderMask) != readers) {
+    __nanosleep(128);
+    if (++spins > kSpinLimit) {
+      atomicExch(p.ws_head + WS_STATUS, 1u);
+      return;
     }
   }
+  p.ws_head[WS_EPOCH] = launch_epoch(eword) << kEpochShift;
 }
 
 // Eight consecutive elements r[tok][j .. j+8) (j a multiple of 8) of THIS launch as four half2 registers: polls the
@@ -592,6 +592,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
   // pushing launch leaves; it is read AFTER the wait for the previous kernels (a launch may start long before its
   // predecessors are complete), by the roles that store outputs.
   uint32_t push_e = 0u;
+  bool closes_epoch = false;   // consumer threads of the CTA that completed r: it advances the workspace's epoch at its end
   // The last n_r_ctas CTAs of the grid only compute r (their copy / aux warps have no tiles): a CTA that ran an R
   // unit AND a full share of row tiles would finish microseconds after the others and set the kernel's length.
   const int n_main = static_cast<int>(gridDim.x) - p.n_r_ctas;
@@ -944,7 +945,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
       rstride = static_cast<int>(gridDim.x);
     }
     if (r_mode == 1 && ru0 >= 0)
-      r_units<NT>(p, ru0, rstride, red, fin, dep_wait_pending, &s_eword, epoch_bar_u32, cx, s_rstd, norm_w != nullptr);
+      r_units<NT>(p, ru0, rstride, red, fin, dep_wait_pending, &s_eword, epoch_bar_u32, cx, s_rstd, norm_w != nullptr, closes_epoch);
     if (threadIdx.x == 0 && r_only) trace_event(p, 6);
     dep_wait(dep_wait_pending);
     if (push_world > 0) push_e = *p.push_epoch + 1u;
@@ -1180,6 +1181,7 @@ gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__
 
   __syncthreads();
   if (threadIdx.x == 0) trace_event(p, 10);
+  if (r_mode == 1 && closes_epoch && threadIdx.x == 0) advance_epoch(p, s_eword);
   if (push_world > 0) {
     // The all-reduce completes inside the launch: CTAs take a ticket when their tiles are stored, and the last few
     // each poll a share of the output's words - every rank's, this one's included - in this rank's buffer until they
