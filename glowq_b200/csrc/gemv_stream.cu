@@ -33,6 +33,7 @@
 //     free of bank conflicts, and the kernel is instantiated per feature set (correction, extras) so that launches
 //     do not carry the code of features they do not use.
 // Every wait (mbarrier, release counter) is bounded; on expiry the kernel records a status word and drains.
+#include <atomic>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -1332,8 +1333,17 @@ cudaError_t launch_gemv_stream(const GemvParams& p, const TensorMaps& tm, int NT
   // K slices stay a run-time property of every instantiation: a decode step mixes sliced (down_proj) and unsliced
   // launches, and alternating between two kernels costs more than the slicing code does (the instruction cache stays
   // warm across back-to-back launches of ONE function: 2.44 against 2.53 ms per Llama-2-13B token step).
+  // ... and once a process has used the extras (a tensor-parallel rank pushes from every other launch), all its
+  // corrected launches take the instantiation with the extras, for the same reason.
+  static std::atomic<bool> extras_seen{false};
+  static const bool sticky = [] {
+    const char* v = std::getenv("GLOWQ_GEMV_STICKY_EXTRAS");
+    return !(v && v[0] == '0');
+  }();
+  const bool extras = p.push_world > 0 || p.norm_w != nullptr;
+  if (extras) extras_seen.store(true, std::memory_order_relaxed);
   const int feat = (p.r_mode != 0 ? kFeatCorr : 0) | kFeatSliced |
-                   ((p.push_world > 0 || p.norm_w != nullptr) ? kFeatExtras : 0);
+                   ((extras || (sticky && p.r_mode != 0 && extras_seen.load(std::memory_order_relaxed))) ? kFeatExtras : 0);
   switch (feat) {
     case kFeatSliced: return launch_feat<kFeatSliced>(p, tm, grid, stream);
     case kFeatSliced | kFeatCorr: return launch_feat<kFeatSliced | kFeatCorr>(p, tm, grid, stream);
