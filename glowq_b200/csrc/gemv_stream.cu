@@ -548,18 +548,18 @@ __device__ __forceinline__ TileInfo tile_info(const GemvParams& p, int tile, int
 #ifndef GLOWQ_GEMV_MIN_CTAS
 #define GLOWQ_GEMV_MIN_CTAS 2   // CTAs per SM the register allocation is bounded for
 #endif
-// FEAT selects what is compiled in: bit 0 the low-rank correction, bit 1 K slices, bit 2 the optional extras (fused
-// input transform, tensor-parallel push).  A launch takes the smallest instantiation the host offers that covers
+// FEAT selects what is compiled in: bit 0 the low-rank correction, bit 1 K slices, bits 2 and 3 the optional extras
+// (tensor-parallel push, fused input transform).  A launch takes the smallest instantiation the host offers that covers
 // it: the code of features that are switched off costs instruction-cache misses and predicated instructions on every
 // launch (the everything-in instantiation is 1.6 times the size of the corrected one and measured 3 % slower on it).
-enum : int { kFeatCorr = 1, kFeatSliced = 2, kFeatExtras = 4 };
+enum : int { kFeatCorr = 1, kFeatSliced = 2, kFeatPush = 4, kFeatNorm = 8 };
 template <int NT, int FEAT>
 __global__ void __launch_bounds__(kGemvThreads, (NT <= 2) ? GLOWQ_GEMV_MIN_CTAS : 1)
 gemv_stream_kernel(const __grid_constant__ GemvParams p, const __grid_constant__ TensorMaps tm) {
   const int r_mode = (FEAT & kFeatCorr) ? p.r_mode : 0;
   const int SK = (FEAT & kFeatSliced) ? p.SK : 1;
-  const int push_world = (FEAT & kFeatExtras) ? p.push_world : 0;
-  const __half* const norm_w = (FEAT & kFeatExtras) ? p.norm_w : nullptr;
+  const int push_world = (FEAT & kFeatPush) ? p.push_world : 0;
+  const __half* const norm_w = (FEAT & kFeatNorm) ? p.norm_w : nullptr;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_abort;
   __shared__ uint32_t s_eword;   // the workspace's epoch word as this CTA's registration found it
@@ -1333,22 +1333,26 @@ cudaError_t launch_gemv_stream(const GemvParams& p, const TensorMaps& tm, int NT
   // K slices stay a run-time property of every instantiation: a decode step mixes sliced (down_proj) and unsliced
   // launches, and alternating between two kernels costs more than the slicing code does (the instruction cache stays
   // warm across back-to-back launches of ONE function: 2.44 against 2.53 ms per Llama-2-13B token step).
-  // ... and once a process has used the extras (a tensor-parallel rank pushes from every other launch), all its
-  // corrected launches take the instantiation with the extras, for the same reason.
-  static std::atomic<bool> extras_seen{false};
+  // ... and once a process has used one of the extras (a tensor-parallel rank pushes from every other launch), all its
+  // corrected launches take the instantiation with it, for the same reason.
+  static std::atomic<int> extras_seen{0};
   static const bool sticky = [] {
     const char* v = std::getenv("GLOWQ_GEMV_STICKY_EXTRAS");
     return !(v && v[0] == '0');
   }();
-  const bool extras = p.push_world > 0 || p.norm_w != nullptr;
-  if (extras) extras_seen.store(true, std::memory_order_relaxed);
-  const int feat = (p.r_mode != 0 ? kFeatCorr : 0) | kFeatSliced |
-                   ((extras || (sticky && p.r_mode != 0 && extras_seen.load(std::memory_order_relaxed))) ? kFeatExtras : 0);
+  int extras = (p.push_world > 0 ? kFeatPush : 0) | (p.norm_w != nullptr ? kFeatNorm : 0);
+  if (extras) extras_seen.fetch_or(extras, std::memory_order_relaxed);
+  if (sticky && p.r_mode != 0) extras |= extras_seen.load(std::memory_order_relaxed);
+  const int feat = (p.r_mode != 0 ? kFeatCorr : 0) | kFeatSliced | extras;
   switch (feat) {
     case kFeatSliced: return launch_feat<kFeatSliced>(p, tm, grid, stream);
     case kFeatSliced | kFeatCorr: return launch_feat<kFeatSliced | kFeatCorr>(p, tm, grid, stream);
-    case kFeatSliced | kFeatExtras: return launch_feat<kFeatSliced | kFeatExtras>(p, tm, grid, stream);
-    default: return launch_feat<kFeatSliced | kFeatCorr | kFeatExtras>(p, tm, grid, stream);
+    case kFeatSliced | kFeatPush: return launch_feat<kFeatSliced | kFeatPush>(p, tm, grid, stream);
+    case kFeatSliced | kFeatPush | kFeatCorr: return launch_feat<kFeatSliced | kFeatPush | kFeatCorr>(p, tm, grid, stream);
+    case kFeatSliced | kFeatNorm: return launch_feat<kFeatSliced | kFeatNorm>(p, tm, grid, stream);
+    case kFeatSliced | kFeatNorm | kFeatCorr: return launch_feat<kFeatSliced | kFeatNorm | kFeatCorr>(p, tm, grid, stream);
+    case kFeatSliced | kFeatPush | kFeatNorm: return launch_feat<kFeatSliced | kFeatPush | kFeatNorm>(p, tm, grid, stream);
+    default: return launch_feat<kFeatSliced | kFeatPush | kFeatNorm | kFeatCorr>(p, tm, grid, stream);
   }
 }
 
