@@ -11,7 +11,10 @@ from glowq_b200.cuda_w4a16 import kernels as K
 from gpu_helpers import Linear, assert_close, dev, ext, make_group, new_out, run_group, status_ok
 
 pytestmark = pytest.mark.gpu
-COMMON = dict(max_examples=25, deadline=None, suppress_health_check=[HealthCheck.too_slow, HealthCheck.data_too_large])
+# derandomize: the same examples on every run (whether the parity suite is green must not depend on the draw; drop
+# the flag when hunting for new cases)
+COMMON = dict(max_examples=40, deadline=None, derandomize=True,
+              suppress_health_check=[HealthCheck.too_slow, HealthCheck.data_too_large])
 
 
 @settings(**COMMON)
